@@ -1,0 +1,288 @@
+// Engine level of the C ABI: continuous batching over the paged KV cache.
+// The reference decodes one sequence at a time (ARCHITECTURE.md:376-377); here up to max_seqs
+// independent `InferenceSession`-equivalent sequences share every launch. Each scheduler step
+// packs one decode row per running sequence plus all prompt rows of newly admitted sequences
+// into one ragged batch, so every layer-op is launched once per step.
+//
+// Block allocation is deterministic: the lowest free block index is handed out first, a
+// sequence reserves ceil(max_total_len/16) blocks at admission and returns them before the
+// next admission once it has finished.
+#include <limits.h>
+
+#include <deque>
+#include <map>
+#include <set>
+
+#include "model.h"
+
+using namespace ak;
+
+namespace {
+
+struct Seq {
+    uint64_t id = 0;
+    std::vector<uint32_t> prompt;
+    uint32_t max_total = 0;
+    std::vector<int32_t> blocks;
+    std::vector<uint32_t> generated;
+    uint32_t cached = 0;  // tokens whose K/V are in the cache
+    int slot = -1;
+    bool finished = false;
+};
+
+}  // namespace
+
+struct ak_engine {
+    ak_ctx* ctx = nullptr;
+    ak_weights* w = nullptr;
+    ak_engine_config cfg{};
+    Runner runner;
+    std::set<int32_t> free_blocks;
+    std::vector<Seq*> slots;     // running sequence per slot (nullptr = free)
+    std::deque<Seq*> waiting;
+    std::map<uint64_t, Seq*> all;
+    uint64_t next_id = 1;
+    ak_engine_stats stats{};
+    unsigned long long launch_base = 0;
+};
+
+static void release(ak_engine* e, Seq* s) {
+    for (int32_t b : s->blocks) e->free_blocks.insert(b);
+    // the block list is kept for ak_engine_block_table on finished sequences
+    if (s->slot >= 0) e->slots[s->slot] = nullptr;
+    s->slot = -1;
+}
+
+extern "C" {
+
+int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak_engine** out) {
+    AK_REQUIRE(ctx && w && cfg && out, AK_ERR_INVALID_ARG, "ak_engine_create: null pointer");
+    AK_REQUIRE(cfg->max_seqs >= 1 && cfg->max_seq_len >= 1, AK_ERR_INVALID_ARG, "ak_engine_create: max_seqs and max_seq_len must be >= 1");
+    AK_REQUIRE(cfg->block_size == 16 || cfg->block_size == 0, AK_ERR_UNSUPPORTED, "ak_engine_create: block_size must be 16");
+    ak_engine* e = new ak_engine();
+    e->ctx = ctx;
+    e->w = w;
+    e->cfg = *cfg;
+    e->cfg.block_size = 16;
+    const uint32_t mb = (cfg->max_seq_len + 15) / 16;
+    if (e->cfg.kv_blocks == 0) e->cfg.kv_blocks = cfg->max_seqs * mb;
+    if (e->cfg.max_batch_tokens < cfg->max_seqs + 1) e->cfg.max_batch_tokens = cfg->max_seqs + cfg->max_seq_len;
+    int rc = e->runner.init(ctx, w, cfg->max_seqs, cfg->max_seq_len, e->cfg.kv_blocks, e->cfg.max_batch_tokens - cfg->max_seqs);
+    if (rc) {
+        delete e;
+        return rc;
+    }
+    e->runner.enable_attn_timing(cfg->attn_timing != 0);
+    for (uint32_t b = 0; b < e->cfg.kv_blocks; b++) e->free_blocks.insert((int32_t)b);
+    e->slots.assign(cfg->max_seqs, nullptr);
+    *out = e;
+    return AK_OK;
+}
+
+int ak_engine_destroy(ak_engine* e) {
+    if (!e) return AK_OK;
+    for (auto& kv : e->all) delete kv.second;
+    delete e;
+    return AK_OK;
+}
+
+int ak_engine_submit(ak_engine* e, const uint32_t* prompt, uint32_t n, uint32_t max_total_len, uint64_t* seq_id) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_submit: null engine");
+    AK_REQUIRE(n != 0, AK_EMPTY_PROMPT, "prompt is empty");
+    AK_REQUIRE(prompt, AK_ERR_INVALID_ARG, "ak_engine_submit: null prompt");
+    AK_REQUIRE(n <= e->cfg.max_seq_len && n <= e->runner.max_prefill_tokens(), AK_PROMPT_TOO_LONG,
+               "prompt is %u tokens, context window is %u (step budget %u)", n, e->cfg.max_seq_len, e->runner.max_prefill_tokens());
+    if (max_total_len > e->cfg.max_seq_len) max_total_len = e->cfg.max_seq_len;
+    AK_REQUIRE(max_total_len > n, AK_CONTEXT_FULL, "context window is full (%u tokens)", max_total_len);
+    Seq* s = new Seq();
+    s->id = e->next_id++;
+    s->prompt.assign(prompt, prompt + n);
+    s->max_total = max_total_len;
+    e->all[s->id] = s;
+    e->waiting.push_back(s);
+    if (seq_id) *seq_id = s->id;
+    return AK_OK;
+}
+
+int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_step: null engine");
+    Runner& r = e->runner;
+    const uint32_t S = e->cfg.max_seqs;
+    const ak_model_config& mc = e->w->cfg;
+    const unsigned long long launches0 = g_launch_count;
+
+    // 1. retire sequences that finished in the previous step (their blocks go back first)
+    for (uint32_t i = 0; i < S; i++)
+        if (e->slots[i] && e->slots[i]->finished) release(e, e->slots[i]);
+
+    // 2. admit waiting sequences in arrival order into the lowest free slots
+    std::vector<Seq*> admitted;
+    uint32_t pf_rows = 0;
+    while (!e->waiting.empty()) {
+        Seq* s = e->waiting.front();
+        int slot = -1;
+        for (uint32_t i = 0; i < S; i++)
+            if (!e->slots[i]) { slot = (int)i; break; }
+        const uint32_t need = (s->max_total + 15) / 16;
+        if (slot < 0 || e->free_blocks.size() < need) break;
+        if (pf_rows + s->prompt.size() > r.max_prefill_tokens()) break;
+        e->waiting.pop_front();
+        s->slot = slot;
+        e->slots[slot] = s;
+        s->blocks.clear();
+        for (uint32_t b = 0; b < need; b++) {
+            auto it = e->free_blocks.begin();
+            s->blocks.push_back(*it);
+            e->free_blocks.erase(it);
+        }
+        int32_t* bt = r.h_block_table(slot);
+        for (uint32_t b = 0; b < r.max_blocks(); b++) bt[b] = b < need ? s->blocks[b] : 0;
+        pf_rows += (uint32_t)s->prompt.size();
+        admitted.push_back(s);
+    }
+
+    // 3. describe the step: decode rows by slot, then the admitted prompts
+    RowInfo* rows = r.h_rows();
+    int32_t* kv = r.h_kv_lens();
+    int32_t* outr = r.h_out_rows();
+    bool any_decode = false;
+    uint32_t max_kv = 1;
+    uint64_t attn_bytes = 0;
+    const uint64_t esz = e->w->dtype == AK_F32 ? 4 : 2;
+    uint32_t n_dec = 0;
+    for (uint32_t i = 0; i < S; i++) {
+        Seq* s = e->slots[i];
+        bool is_new = false;
+        for (Seq* a : admitted) is_new |= (a == s);
+        if (s && !is_new && !s->finished) {
+            const uint32_t pos = s->cached;
+            rows[i] = {-(int32_t)(i + 1), (int32_t)pos, s->blocks[pos / 16] * 16 + (int32_t)(pos % 16), (int32_t)i};
+            kv[i] = (int32_t)(pos + 1);
+            outr[i] = (int32_t)i;
+            any_decode = true;
+            n_dec++;
+            if (pos + 1 > max_kv) max_kv = pos + 1;
+            attn_bytes += (uint64_t)(pos + 1) * mc.dim * 2 * esz + (uint64_t)mc.dim * 2 * esz + (uint64_t)((pos + 16) / 16) * 4;
+        } else {
+            rows[i] = {INT_MIN, -1, -1, (int32_t)i};
+            kv[i] = 0;
+            outr[i] = -1;
+        }
+    }
+    uint32_t row = S, max_pf = 0;
+    int32_t* cu = r.h_pf_cu();
+    int32_t* pfs = r.h_pf_slot();
+    cu[0] = 0;
+    for (size_t a = 0; a < admitted.size(); a++) {
+        Seq* s = admitted[a];
+        const uint32_t P = (uint32_t)s->prompt.size();
+        for (uint32_t j = 0; j < P; j++) {
+            uint32_t t = s->prompt[j];
+            rows[row + j] = {t > 0x7fffffffu ? INT_MAX : (int32_t)t, (int32_t)j, s->blocks[j / 16] * 16 + (int32_t)(j % 16), s->slot};
+        }
+        row += P;
+        cu[a + 1] = (int32_t)(row - S);
+        pfs[a] = s->slot;
+        outr[s->slot] = (int32_t)(row - 1);
+        if (P > max_pf) max_pf = P;
+    }
+    if (!any_decode && admitted.empty()) {
+        if (n_running) *n_running = 0;
+        if (n_waiting) *n_waiting = (uint32_t)e->waiting.size();
+        return AK_OK;
+    }
+
+    // 4. launch
+    int rc;
+    const bool graph = e->cfg.use_cuda_graph && admitted.empty();
+    if (graph) rc = r.run_decode_graph(max_kv);
+    else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
+    if (rc) return rc;
+    rc = r.sync();
+    if (rc) return rc;
+
+    // 5. collect this step's tokens
+    const uint32_t* sampled = r.h_sampled();
+    uint32_t running = 0;
+    for (uint32_t i = 0; i < S; i++) {
+        Seq* s = e->slots[i];
+        if (!s || s->finished) continue;
+        bool is_new = false;
+        for (Seq* a : admitted) is_new |= (a == s);
+        s->cached = is_new ? (uint32_t)s->prompt.size() : s->cached + 1;
+        const uint32_t tok = sampled[i];
+        s->generated.push_back(tok);
+        const uint32_t total = (uint32_t)(s->prompt.size() + s->generated.size());
+        if (total >= s->max_total || (e->cfg.stop_on_eos && tok == mc.eos_token)) s->finished = true;
+        else running++;
+    }
+    e->stats.steps++;
+    e->stats.decode_tokens += n_dec;
+    e->stats.prefill_tokens += pf_rows;
+    if (graph) e->stats.graph_launches++; else e->stats.eager_steps++;
+    e->stats.kernel_launches += (g_launch_count - launches0);
+    if (e->cfg.attn_timing && any_decode) {
+        float ms = r.last_attn_ms();
+        if (ms > 0.0f) {
+            e->stats.attn_ms_total += ms;
+            e->stats.attn_launches_timed++;
+            e->stats.attn_bytes_total += attn_bytes;
+        }
+    }
+    if (n_running) *n_running = running;
+    if (n_waiting) *n_waiting = (uint32_t)e->waiting.size();
+    return AK_OK;
+}
+
+int ak_engine_poll(ak_engine* e, uint64_t seq_id, uint32_t* out, uint32_t cap, uint32_t* n_out, int* finished) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_poll: null engine");
+    auto it = e->all.find(seq_id);
+    AK_REQUIRE(it != e->all.end(), AK_ERR_NOT_FOUND, "ak_engine_poll: unknown sequence %llu", (unsigned long long)seq_id);
+    Seq* s = it->second;
+    uint32_t n = (uint32_t)s->generated.size();
+    if (out)
+        for (uint32_t i = 0; i < n && i < cap; i++) out[i] = s->generated[i];
+    if (n_out) *n_out = n;
+    if (finished) *finished = s->finished ? 1 : 0;
+    return AK_OK;
+}
+
+int ak_engine_block_table(ak_engine* e, uint64_t seq_id, int32_t* out, uint32_t cap, uint32_t* n_out) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_block_table: null engine");
+    auto it = e->all.find(seq_id);
+    AK_REQUIRE(it != e->all.end(), AK_ERR_NOT_FOUND, "ak_engine_block_table: unknown sequence %llu", (unsigned long long)seq_id);
+    Seq* s = it->second;
+    uint32_t n = (uint32_t)s->blocks.size();
+    if (out)
+        for (uint32_t i = 0; i < n && i < cap; i++) out[i] = s->blocks[i];
+    if (n_out) *n_out = n;
+    return AK_OK;
+}
+
+int ak_engine_clear_finished(ak_engine* e) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_clear_finished: null engine");
+    for (auto it = e->all.begin(); it != e->all.end();) {
+        Seq* s = it->second;
+        if (s->finished) {
+            if (s->slot >= 0) release(e, s);
+            delete s;
+            it = e->all.erase(it);
+        } else {
+            ++it;
+        }
+    }
+    return AK_OK;
+}
+
+int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out) {
+    AK_REQUIRE(e && out, AK_ERR_INVALID_ARG, "ak_engine_get_stats: null pointer");
+    *out = e->stats;
+    return AK_OK;
+}
+int ak_engine_reset_stats(ak_engine* e) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_reset_stats: null engine");
+    e->stats = ak_engine_stats{};
+    return AK_OK;
+}
+
+}  // extern "C"

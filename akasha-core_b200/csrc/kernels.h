@@ -1,0 +1,75 @@
+// Internal launcher interface between the kernels (*.cu) and the host runtime
+// (runner / session / engine). All pointers are device pointers unless named *_host.
+#pragma once
+#include "common.cuh"
+
+namespace ak {
+
+// ---- elementwise.cu ----------------------------------------------------------------------
+// Token source per row: tok_src[r] >= 0 is a literal id; tok_src[r] < 0 means "the token last
+// sampled for sequence slot -(tok_src[r]+1)". Rows with slot_of_row[r] < 0 are zero-filled.
+// idx_stride: distance (in int32) between consecutive rows' entries of tok_src / positions / slots.
+int launch_embed_rows(cudaStream_t st, const int32_t* tok_src, uint32_t idx_stride, const uint32_t* sampled,
+                      const void* table, uint32_t table_dtype, float* hidden, uint32_t vocab, uint32_t dim,
+                      uint32_t rows);
+// y[r] = rmsnorm(x[row_map ? row_map[r] : r]) * w ; rows whose mapped index is < 0 are zeroed.
+int launch_rmsnorm(cudaStream_t st, const float* x, const float* w, void* y, uint32_t out_dtype,
+                   const int32_t* row_map, uint32_t rows, uint32_t size, float eps);
+int launch_rmsnorm_rope_residual(cudaStream_t st, float* x, const float* residual, const float* w, void* y,
+                                 const int32_t* positions, uint32_t rows, uint32_t size, float eps,
+                                 uint32_t head_dim, uint32_t out_dtype);
+// qkv [T,3*dim] f32 -> q_out [T,dim] (q_dtype) with RoPE; K (RoPE) and V appended at slots[].
+// rope_table: [max_pos][head_dim/2] float2 (cos,sin) or NULL (compute on device).
+int launch_rope_kv_append(cudaStream_t st, const float* qkv, const int32_t* positions, const int32_t* slots,
+                          uint32_t idx_stride, void* q_out, void* k_pool, void* v_pool, const float2* rope_table,
+                          uint32_t rope_table_len, uint32_t tokens, uint32_t heads, uint32_t head_dim,
+                          uint32_t block_size, uint32_t kv_dtype);
+// Greedy argmax per row (first maximum wins). row_active: NULL or int32[rows]; rows with a
+// negative entry keep their previous out_idx.
+int launch_argmax(cudaStream_t st, const float* logits, uint32_t rows, uint32_t n, uint32_t ld,
+                  const int32_t* row_active, uint32_t* out_idx);
+int launch_silu(cudaStream_t st, float* x, uint64_t n);
+int launch_f32_to_bf16(cudaStream_t st, const float* src, void* dst, uint64_t n);
+int launch_bf16_to_f32(cudaStream_t st, const void* src, float* dst, uint64_t n);
+int launch_transpose_to_bf16(cudaStream_t st, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);
+int launch_transpose_from_bf16(cudaStream_t st, const void* wt_nk, float* w_kn, uint32_t k, uint32_t n);
+int launch_fill_normal(cudaStream_t st, void* dst, uint32_t dtype, uint64_t n, uint64_t seed, uint64_t stream_id,
+                       float mean, float std);
+// Gather a sequence's paged rows back into the reference's contiguous [len, heads*head_dim] f32.
+int launch_gather_paged(cudaStream_t st, const void* pool, uint32_t kv_dtype, const int32_t* block_table,
+                        float* out, uint32_t len, uint32_t heads, uint32_t head_dim, uint32_t block_size);
+
+// ---- gemm_simt.cu (true fp32) ---------------------------------------------------------------
+enum { GEMM_ADD = 1, GEMM_SILU = 2 };
+// C[m,n] (+)= A[m,k] @ B[k,n], row-major f32. m == 1 uses the cluster split-K GEMV.
+int launch_gemm_f32(cudaStream_t st, const float* a, const float* b, float* c, uint32_t m, uint32_t n,
+                    uint32_t k, uint32_t flags);
+
+// ---- gemm_tcgen05.cu (bf16 tensor cores) --------------------------------------------------------
+int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n,
+                     uint32_t k, uint32_t epilogue, uint32_t ldc);
+int gemm_bf16_check_status(cudaStream_t st);  // reads the device status word (syncs the stream)
+
+// ---- attn_decode.cu ----------------------------------------------------------------------------
+size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t n_splits);
+uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t max_kv_len);
+int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+                             const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                             const ak_attn_decode_params& p);
+
+int attn_decode_status(unsigned int* out);  // device status word of the decode kernel
+
+// ---- attn_prefill.cu ---------------------------------------------------------------------------
+// Causal varlen attention over newly prefilled sequences. q/out rows of sequence i are
+// [cu[i], cu[i+1]) (+ row_base); K/V are read from the paged pools through the sequence's
+// block table (block_tables[seq_slot[i]]). Query row j of a sequence sits at position j.
+int launch_attn_prefill_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+                              const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
+                              const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len,
+                              uint32_t row_base, uint32_t heads, uint32_t head_dim, uint32_t block_size,
+                              float scale, uint32_t dtype);
+// The reference emitter's contiguous form (f32 q/k/v [*,dim], optional l_cache).
+int launch_flash_attention_f32(cudaStream_t st, const float* q, const float* k, const float* v, float* out,
+                               float* l_cache, ak_flash_attn_meta m);
+
+}  // namespace ak

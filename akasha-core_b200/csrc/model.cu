@@ -1,0 +1,426 @@
+// Context, weights (ModelWeights layout, src/nn/weights.rs:32-171) and the ragged-batch runner.
+#include "model.h"
+
+#include <math.h>
+#include <string.h>
+
+using namespace ak;
+
+// ======================================================================== context
+extern "C" {
+
+int ak_ctx_create(int device, ak_ctx** out) {
+    AK_REQUIRE(out, AK_ERR_INVALID_ARG, "ak_ctx_create: null pointer");
+    int n = 0;
+    AK_CUDA(cudaGetDeviceCount(&n));
+    AK_REQUIRE(device >= 0 && device < n, AK_ERR_INVALID_ARG, "ak_ctx_create: device %d out of range (%d present)", device, n);
+    AK_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    AK_CUDA(cudaGetDeviceProperties(&prop, device));
+    AK_REQUIRE(prop.major == 10, AK_ERR_UNSUPPORTED,
+               "ak_ctx_create: device %d is sm_%d%d; this library is built for sm_100a (B200) only", device, prop.major, prop.minor);
+    ak_ctx* c = new ak_ctx();
+    c->device = device;
+    AK_CUDA(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    *out = c;
+    return AK_OK;
+}
+int ak_ctx_destroy(ak_ctx* ctx) {
+    if (!ctx) return AK_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return AK_OK;
+}
+int ak_ctx_synchronize(ak_ctx* ctx) {
+    AK_REQUIRE(ctx, AK_ERR_INVALID_ARG, "ak_ctx_synchronize: null ctx");
+    AK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AK_OK;
+}
+void* ak_ctx_stream(ak_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+// ======================================================================== weights
+static size_t welem(uint32_t dtype) { return dtype == AK_F32 ? 4 : 2; }
+
+int ak_weights_create(ak_ctx* ctx, const ak_model_config* cfg, uint32_t dtype, ak_weights** out) {
+    AK_REQUIRE(ctx && cfg && out, AK_ERR_INVALID_ARG, "ak_weights_create: null pointer");
+    AK_REQUIRE(dtype <= AK_BF16, AK_ERR_INVALID_ARG, "ak_weights_create: bad dtype %u", dtype);
+    AK_REQUIRE(cfg->num_layers >= 1 && cfg->num_heads >= 1 && cfg->dim % cfg->num_heads == 0 && cfg->vocab_size >= 1 && cfg->ffn_hidden >= 1,
+               AK_ERR_INVALID_ARG, "ak_weights_create: bad config (layers >= 1, dim %% heads == 0 required)");
+    const uint32_t hd = cfg->dim / cfg->num_heads;
+    AK_REQUIRE(hd % 2 == 0, AK_ERR_INVALID_ARG, "ak_weights_create: head_dim must be even (RoPE pairs)");
+    if (dtype == AK_BF16)
+        AK_REQUIRE(cfg->dim % 8 == 0 && cfg->ffn_hidden % 8 == 0 && hd % 8 == 0, AK_ERR_UNSUPPORTED,
+                   "ak_weights_create: bf16 mode needs dim, ffn_hidden and head_dim to be multiples of 8");
+    else
+        AK_REQUIRE(hd % 4 == 0, AK_ERR_UNSUPPORTED, "ak_weights_create: head_dim must be a multiple of 4");
+    AK_CUDA(cudaSetDevice(ctx->device));
+    ak_weights* w = new ak_weights();
+    w->ctx = ctx;
+    w->cfg = *cfg;
+    w->dtype = dtype;
+    const uint64_t V = cfg->vocab_size, D = cfg->dim, F = cfg->ffn_hidden;
+    w->blocks.resize(cfg->num_layers);
+    auto add = [&](void** p, uint64_t len, uint32_t kind, uint32_t in, uint32_t o) { w->params.push_back({p, len, kind, in, o}); };
+    add(&w->embedding, V * D, 1, (uint32_t)V, (uint32_t)D);
+    for (auto& b : w->blocks) {
+        add((void**)&b.norm_1, D, 0, 0, 0);
+        add(&b.qkv, D * 3 * D, 2, (uint32_t)D, (uint32_t)(3 * D));
+        add(&b.out, D * D, 2, (uint32_t)D, (uint32_t)D);
+        add((void**)&b.norm_2, D, 0, 0, 0);
+        add(&b.up, D * F, 2, (uint32_t)D, (uint32_t)F);
+        add(&b.down, F * D, 2, (uint32_t)F, (uint32_t)D);
+    }
+    add((void**)&w->final_norm, D, 0, 0, 0);
+    add(&w->lm_head, D * V, 2, (uint32_t)D, (uint32_t)V);
+    for (auto& pr : w->params) {
+        size_t bytes = pr.len * (pr.kind == 0 ? 4 : welem(dtype));
+        cudaError_t e = cudaMalloc(pr.ptr, bytes);
+        if (e != cudaSuccess) {
+            ak_weights_destroy(w);
+            return cuda_fail(e, "cudaMalloc(weights)", __FILE__, __LINE__);
+        }
+        cudaMemsetAsync(*pr.ptr, 0, bytes, ctx->stream);
+    }
+    AK_CUDA(cudaStreamSynchronize(ctx->stream));
+    *out = w;
+    return AK_OK;
+}
+
+int ak_weights_destroy(ak_weights* w) {
+    if (!w) return AK_OK;
+    cudaSetDevice(w->ctx->device);
+    for (auto& pr : w->params)
+        if (*pr.ptr) cudaFree(*pr.ptr);
+    if (w->staging) cudaFree(w->staging);
+    delete w;
+    return AK_OK;
+}
+
+uint32_t ak_weights_param_count(const ak_weights* w) { return w ? (uint32_t)w->params.size() : 0; }
+uint64_t ak_weights_param_len(const ak_weights* w, uint32_t index) {
+    return (w && index < w->params.size()) ? w->params[index].len : 0;
+}
+
+static int ensure_staging(ak_weights* w, size_t elems) {
+    if (w->staging_elems >= elems) return AK_OK;
+    if (w->staging) cudaFree(w->staging);
+    w->staging = nullptr;
+    w->staging_elems = 0;
+    AK_CUDA(cudaMalloc((void**)&w->staging, elems * sizeof(float)));
+    w->staging_elems = elems;
+    return AK_OK;
+}
+
+int ak_weights_set_param(ak_weights* w, uint32_t index, const float* host, uint64_t n_elems) {
+    AK_REQUIRE(w && host, AK_ERR_INVALID_ARG, "ak_weights_set_param: null pointer");
+    AK_REQUIRE(index < w->params.size(), AK_ERR_INVALID_ARG, "ak_weights_set_param: index %u out of range", index);
+    auto& pr = w->params[index];
+    AK_REQUIRE(n_elems == pr.len, AK_ERR_INVALID_ARG, "ak_weights_set_param: tensor %u holds %llu elements, got %llu", index,
+               (unsigned long long)pr.len, (unsigned long long)n_elems);
+    AK_CUDA(cudaSetDevice(w->ctx->device));
+    cudaStream_t st = w->ctx->stream;
+    if (w->dtype == AK_F32 || pr.kind == 0) {
+        AK_CUDA(cudaMemcpyAsync(*pr.ptr, host, pr.len * 4, cudaMemcpyHostToDevice, st));
+    } else {
+        int rc = ensure_staging(w, pr.len);
+        if (rc) return rc;
+        AK_CUDA(cudaMemcpyAsync(w->staging, host, pr.len * 4, cudaMemcpyHostToDevice, st));
+        rc = (pr.kind == 1) ? launch_f32_to_bf16(st, w->staging, *pr.ptr, pr.len)
+                            : launch_transpose_to_bf16(st, w->staging, *pr.ptr, pr.in, pr.out);
+        if (rc) return rc;
+    }
+    AK_CUDA(cudaStreamSynchronize(st));
+    return AK_OK;
+}
+
+int ak_weights_get_param(ak_weights* w, uint32_t index, float* host, uint64_t n_elems) {
+    AK_REQUIRE(w && host, AK_ERR_INVALID_ARG, "ak_weights_get_param: null pointer");
+    AK_REQUIRE(index < w->params.size(), AK_ERR_INVALID_ARG, "ak_weights_get_param: index %u out of range", index);
+    auto& pr = w->params[index];
+    AK_REQUIRE(n_elems == pr.len, AK_ERR_INVALID_ARG, "ak_weights_get_param: tensor %u holds %llu elements", index, (unsigned long long)pr.len);
+    AK_CUDA(cudaSetDevice(w->ctx->device));
+    cudaStream_t st = w->ctx->stream;
+    if (w->dtype == AK_F32 || pr.kind == 0) {
+        AK_CUDA(cudaMemcpyAsync(host, *pr.ptr, pr.len * 4, cudaMemcpyDeviceToHost, st));
+    } else {
+        int rc = ensure_staging(w, pr.len);
+        if (rc) return rc;
+        rc = (pr.kind == 1) ? launch_bf16_to_f32(st, *pr.ptr, w->staging, pr.len)
+                            : launch_transpose_from_bf16(st, *pr.ptr, w->staging, pr.in, pr.out);
+        if (rc) return rc;
+        AK_CUDA(cudaMemcpyAsync(host, w->staging, pr.len * 4, cudaMemcpyDeviceToHost, st));
+    }
+    AK_CUDA(cudaStreamSynchronize(st));
+    return AK_OK;
+}
+
+int ak_weights_init_synthetic(ak_weights* w, uint64_t seed, float std) {
+    AK_REQUIRE(w, AK_ERR_INVALID_ARG, "ak_weights_init_synthetic: null pointer");
+    AK_CUDA(cudaSetDevice(w->ctx->device));
+    for (size_t i = 0; i < w->params.size(); i++) {
+        auto& pr = w->params[i];
+        int rc = launch_fill_normal(w->ctx->stream, *pr.ptr, pr.kind == 0 ? (uint32_t)AK_F32 : w->dtype, pr.len, seed, i,
+                                    pr.kind == 0 ? 1.0f : 0.0f, std);
+        if (rc) return rc;
+    }
+    AK_CUDA(cudaStreamSynchronize(w->ctx->stream));
+    return AK_OK;
+}
+
+}  // extern "C"
+
+// ======================================================================== runner
+namespace ak {
+
+static uint32_t align_up(uint32_t v, uint32_t a) { return (v + a - 1) / a * a; }
+
+Runner::~Runner() {
+    if (!ctx_) return;
+    cudaSetDevice(ctx_->device);
+    cudaStreamSynchronize(ctx_->stream);
+    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    if (ev_attn0_) cudaEventDestroy(ev_attn0_);
+    if (ev_attn1_) cudaEventDestroy(ev_attn1_);
+    for (void* p : k_pool_) cudaFree(p);
+    for (void* p : v_pool_) cudaFree(p);
+    cudaFree(hidden_); cudaFree(xn_); cudaFree(qkv_); cudaFree(qbuf_); cudaFree(attn_); cudaFree(up_);
+    cudaFree(xf_); cudaFree(logits_); cudaFree(attn_scratch_); cudaFree(rope_table_);
+    cudaFree(d_desc_); cudaFree(d_sampled_);
+    if (h_desc_) cudaFreeHost(h_desc_);
+    if (h_sampled_) cudaFreeHost(h_sampled_);
+}
+
+int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq_len, uint32_t kv_blocks, uint32_t max_prefill_tokens) {
+    ctx_ = ctx;
+    w_ = w;
+    AK_CUDA(cudaSetDevice(ctx->device));
+    const ak_model_config& c = w->cfg;
+    const uint32_t D = c.dim, F = c.ffn_hidden, V = c.vocab_size, H = c.num_heads, hd = D / H;
+    max_seqs_ = max_seqs;
+    max_seq_len_ = max_seq_len;
+    max_blocks_ = (max_seq_len + 15) / 16;
+    n_blocks_ = kv_blocks ? kv_blocks : max_seqs * max_blocks_;
+    max_pf_tokens_ = max_prefill_tokens;
+    max_rows_ = max_seqs + max_prefill_tokens;
+    const size_t act = welem(w->dtype);
+
+    d_.kv_lens = 0;
+    d_.out_rows = d_.kv_lens + max_seqs;
+    d_.pf_cu = d_.out_rows + max_seqs;
+    d_.pf_slot = d_.pf_cu + max_seqs + 1;
+    d_.block_tables = d_.pf_slot + max_seqs;
+    d_.rows = align_up(d_.block_tables + max_seqs * max_blocks_, 4);
+    d_.total = d_.rows + max_rows_ * 4;
+    AK_CUDA(cudaMallocHost((void**)&h_desc_, (size_t)d_.total * 4));
+    memset(h_desc_, 0, (size_t)d_.total * 4);
+    AK_CUDA(cudaMalloc((void**)&d_desc_, (size_t)d_.total * 4));
+    AK_CUDA(cudaMemset(d_desc_, 0, (size_t)d_.total * 4));
+    AK_CUDA(cudaMallocHost((void**)&h_sampled_, (size_t)max_seqs * 4));
+    memset(h_sampled_, 0, (size_t)max_seqs * 4);
+    AK_CUDA(cudaMalloc((void**)&d_sampled_, (size_t)max_seqs * 4));
+    AK_CUDA(cudaMemset(d_sampled_, 0, (size_t)max_seqs * 4));
+
+    const size_t pool_bytes = (size_t)n_blocks_ * H * 16 * hd * act;
+    k_pool_.assign(c.num_layers, nullptr);
+    v_pool_.assign(c.num_layers, nullptr);
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        AK_CUDA(cudaMalloc(&k_pool_[l], pool_bytes));
+        AK_CUDA(cudaMalloc(&v_pool_[l], pool_bytes));
+        AK_CUDA(cudaMemsetAsync(k_pool_[l], 0, pool_bytes, ctx->stream));
+        AK_CUDA(cudaMemsetAsync(v_pool_[l], 0, pool_bytes, ctx->stream));
+    }
+    const size_t R = max_rows_;
+    AK_CUDA(cudaMalloc((void**)&hidden_, R * D * 4));
+    AK_CUDA(cudaMalloc(&xn_, R * D * act));
+    AK_CUDA(cudaMalloc((void**)&qkv_, R * 3 * D * 4));
+    AK_CUDA(cudaMalloc(&qbuf_, R * D * act));
+    AK_CUDA(cudaMalloc(&attn_, R * D * act));
+    AK_CUDA(cudaMalloc(&up_, R * F * act));
+    AK_CUDA(cudaMalloc(&xf_, (size_t)max_seqs * D * act));
+    AK_CUDA(cudaMalloc((void**)&logits_, (size_t)max_seqs * V * 4));
+    AK_CUDA(cudaMemsetAsync(hidden_, 0, R * D * 4, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(xn_, 0, R * D * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(qkv_, 0, R * 3 * D * 4, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(qbuf_, 0, R * D * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(attn_, 0, R * D * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(up_, 0, R * F * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(logits_, 0, (size_t)max_seqs * V * 4, ctx->stream));
+    attn_scratch_bytes_ = attn_decode_scratch_bytes(max_seqs, H, hd, 32);
+    AK_CUDA(cudaMalloc((void**)&attn_scratch_, attn_scratch_bytes_));
+
+    // RoPE factors from the host libm, exactly as the reference's CPU kernel forms them
+    // (src/shaders/cpu.rs:98-100): freq = 1/powf(10000, d/hd), angle = (float)pos * freq.
+    rope_len_ = max_seq_len;
+    std::vector<float2> tab((size_t)rope_len_ * (hd / 2));
+    for (uint32_t pos = 0; pos < rope_len_; pos++)
+        for (uint32_t d = 0; d < hd; d += 2) {
+            float freq = 1.0f / powf(10000.0f, (float)d / (float)hd);
+            float angle = (float)pos * freq;
+            tab[(size_t)pos * (hd / 2) + d / 2] = make_float2(cosf(angle), sinf(angle));
+        }
+    AK_CUDA(cudaMalloc((void**)&rope_table_, tab.size() * sizeof(float2)));
+    AK_CUDA(cudaMemcpyAsync(rope_table_, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, ctx->stream));
+    AK_CUDA(cudaEventCreate(&ev_attn0_));
+    AK_CUDA(cudaEventCreate(&ev_attn1_));
+    AK_CUDA(cudaStreamSynchronize(ctx->stream));
+    return AK_OK;
+}
+
+// mode: 0 store f32, 1 add into f32, 2 silu -> activation dtype
+int Runner::gemm(const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k, int mode) {
+    cudaStream_t st = ctx_->stream;
+    if (w_->dtype == AK_F32) {
+        uint32_t flags = mode == 1 ? GEMM_ADD : (mode == 2 ? GEMM_SILU : 0);
+        return launch_gemm_f32(st, (const float*)a, (const float*)wt, (float*)c, m, n, k, flags);
+    }
+    uint32_t epi = mode == 1 ? AK_EPI_ADD_F32 : (mode == 2 ? AK_EPI_SILU_BF16 : AK_EPI_STORE_F32);
+    return launch_gemm_bf16(st, a, wt, c, m, n, k, epi, n);
+}
+
+int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode,
+                          uint32_t n_splits, bool capturing) {
+    cudaStream_t st = ctx_->stream;
+    const ak_model_config& c = w_->cfg;
+    const uint32_t D = c.dim, F = c.ffn_hidden, V = c.vocab_size, H = c.num_heads, hd = D / H;
+    const uint32_t dt = w_->dtype;
+    const float scale = 1.0f / sqrtf((float)hd);
+    const int32_t* rows = d_desc_ + d_.rows;
+    int rc;
+#define RC(x) do { rc = (x); if (rc) return rc; } while (0)
+    RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
+    for (uint32_t l = 0; l < c.num_layers; l++) {
+        const auto& b = w_->blocks[l];
+        RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
+        RC(gemm(xn_, b.qkv, qkv_, T, 3 * D, D, 0));
+        RC(launch_rope_kv_append(st, qkv_, rows + 1, rows + 2, 4, qbuf_, k_pool_[l], v_pool_[l], rope_table_, rope_len_, T, H, hd, 16, dt));
+        if (any_decode) {
+            ak_attn_decode_params p{};
+            p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
+            p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
+            const bool timed = attn_timing_ && l == 0;
+            if (timed) {
+                if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, st, cudaEventRecordExternal));
+                else AK_CUDA(cudaEventRecord(ev_attn0_, st));
+            }
+            RC(launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p));
+            if (timed) {
+                if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, st, cudaEventRecordExternal));
+                else AK_CUDA(cudaEventRecord(ev_attn1_, st));
+                ev_valid_ = true;
+            }
+        }
+        if (n_pf_seqs) {
+            RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
+                                         d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt));
+        }
+        RC(gemm(attn_, b.out, hidden_, T, D, D, 1));
+        RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
+        RC(gemm(xn_, b.up, up_, T, F, D, 2));
+        RC(gemm(up_, b.down, hidden_, T, D, F, 1));
+    }
+    RC(launch_rmsnorm(st, hidden_, w_->final_norm, xf_, dt, d_desc_ + d_.out_rows, max_seqs_, D, c.norm_eps));
+    RC(gemm(xf_, w_->lm_head, logits_, max_seqs_, V, D, 0));
+    RC(launch_argmax(st, logits_, max_seqs_, V, V, d_desc_ + d_.out_rows, d_sampled_));
+#undef RC
+    (void)n_pf_rows;
+    return AK_OK;
+}
+
+int Runner::run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t max_kv_len) {
+    AK_REQUIRE(n_prefill_rows <= max_pf_tokens_, AK_ERR_INVALID_ARG, "runner: %u prefill rows exceed the step budget %u", n_prefill_rows, max_pf_tokens_);
+    AK_CUDA(cudaSetDevice(ctx_->device));
+    cudaStream_t st = ctx_->stream;
+    const uint32_t T = max_seqs_ + n_prefill_rows;
+    const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
+    AK_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st));
+    // One split count per runner (from the longest sequence it can hold): eager and captured
+    // steps then sum in the same order, so a sequence's tokens do not depend on its neighbours.
+    (void)max_kv_len;
+    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
+    int rc = launch_layers(T, n_prefill_rows, n_pf_seqs, max_pf_len, any_decode, n_splits, false);
+    if (rc) return rc;
+    AK_CUDA(cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st));
+    eager_steps++;
+    return AK_OK;
+}
+
+int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
+    AK_CUDA(cudaSetDevice(ctx_->device));
+    cudaStream_t st = ctx_->stream;
+    const uint32_t H = w_->cfg.num_heads;
+    // The split count is baked into the captured launch; it is chosen once from the longest
+    // sequence the runner can hold.
+    (void)max_kv_len_hint;
+    if (!graph_exec_) {
+        // one eager pass first: sets kernel attributes and faults early outside capture
+        int rc = run(0, 0, 0, true, max_seq_len_);
+        if (rc) return rc;
+        AK_CUDA(cudaStreamSynchronize(st));
+        graph_splits_ = attn_decode_pick_splits(max_seqs_, H, max_seq_len_);
+        cudaGraph_t graph = nullptr;
+        AK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        const size_t bytes = ((size_t)d_.rows + (size_t)max_seqs_ * 4) * 4;
+        cudaError_t e = cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st);
+        rc = (e == cudaSuccess) ? launch_layers(max_seqs_, 0, 0, 0, true, graph_splits_, true) : AK_ERR_CUDA;
+        if (rc == AK_OK) e = cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st);
+        cudaError_t e2 = cudaStreamEndCapture(st, &graph);
+        if (rc) return rc;
+        if (e != cudaSuccess) return cuda_fail(e, "capture memcpy", __FILE__, __LINE__);
+        if (e2 != cudaSuccess) return cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
+        AK_CUDA(cudaGraphInstantiate(&graph_exec_, graph, 0));
+        cudaGraphDestroy(graph);
+        // The eager pass above already executed this step: do not run it twice.
+        return AK_OK;
+    }
+    AK_CUDA(cudaGraphLaunch(graph_exec_, st));
+    graph_launches++;
+    return AK_OK;
+}
+
+int Runner::sync() {
+    AK_CUDA(cudaStreamSynchronize(ctx_->stream));
+    return AK_OK;
+}
+
+float Runner::last_attn_ms() {
+    if (!ev_valid_) return 0.0f;
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, ev_attn0_, ev_attn1_) != cudaSuccess) {
+        cudaGetLastError();
+        return 0.0f;
+    }
+    return ms;
+}
+
+int Runner::read_logits(uint32_t slot, float* host_out) {
+    const uint32_t V = w_->cfg.vocab_size;
+    AK_CUDA(cudaMemcpyAsync(host_out, logits_ + (size_t)slot * V, (size_t)V * 4, cudaMemcpyDeviceToHost, ctx_->stream));
+    AK_CUDA(cudaStreamSynchronize(ctx_->stream));
+    return AK_OK;
+}
+
+int Runner::gather_cache(uint32_t layer, const int32_t* h_table, uint32_t len, float* k_out, float* v_out) {
+    if (len == 0) return AK_OK;
+    cudaStream_t st = ctx_->stream;
+    const uint32_t D = w_->cfg.dim, H = w_->cfg.num_heads, hd = D / H;
+    const uint32_t nb = (len + 15) / 16;
+    int32_t* d_table = nullptr;
+    float* d_out = nullptr;
+    AK_CUDA(cudaMalloc((void**)&d_table, (size_t)nb * 4));
+    AK_CUDA(cudaMalloc((void**)&d_out, (size_t)len * D * 4));
+    AK_CUDA(cudaMemcpyAsync(d_table, h_table, (size_t)nb * 4, cudaMemcpyHostToDevice, st));
+    int rc = AK_OK;
+    for (int which = 0; which < 2 && rc == AK_OK; which++) {
+        float* dst = which == 0 ? k_out : v_out;
+        if (!dst) continue;
+        rc = launch_gather_paged(st, which == 0 ? k_pool_[layer] : v_pool_[layer], w_->dtype, d_table, d_out, len, H, hd, 16);
+        if (rc == AK_OK && cudaMemcpyAsync(dst, d_out, (size_t)len * D * 4, cudaMemcpyDeviceToHost, st) != cudaSuccess) rc = AK_ERR_CUDA;
+        if (rc == AK_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = AK_ERR_CUDA;
+    }
+    cudaFree(d_table);
+    cudaFree(d_out);
+    return rc;
+}
+
+}  // namespace ak

@@ -1,0 +1,123 @@
+// Host runtime shared by the session and engine levels of the C ABI: context, weights in the
+// `ModelWeights::params()` order, and the ragged-batch runner that launches one kernel per
+// layer-op over all token rows of a step.
+#pragma once
+#include <vector>
+
+#include "kernels.h"
+
+struct ak_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+};
+
+struct ak_weights {
+    ak_ctx* ctx = nullptr;
+    ak_model_config cfg{};
+    uint32_t dtype = AK_F32;
+    // Device tensors. f32 mode: matrices f32 [in,out] (the reference layout, src/nn/weights.rs:32-47).
+    // bf16 mode: embedding bf16 [vocab,dim]; projection matrices bf16 [out,in] (transposed once at
+    // upload so both tcgen05 operands are K-major); norm gains stay f32.
+    void* embedding = nullptr;
+    struct Block {
+        float* norm_1 = nullptr;
+        void* qkv = nullptr;
+        void* out = nullptr;
+        float* norm_2 = nullptr;
+        void* up = nullptr;
+        void* down = nullptr;
+    };
+    std::vector<Block> blocks;
+    float* final_norm = nullptr;
+    void* lm_head = nullptr;
+    float* staging = nullptr;  // f32 staging for layout conversion
+    size_t staging_elems = 0;
+
+    struct ParamRef {
+        void** ptr;
+        uint64_t len;
+        uint32_t kind;  // 0 = norm gain (f32), 1 = embedding table, 2 = matrix [in,out]
+        uint32_t in, out;
+    };
+    std::vector<ParamRef> params;  // params() order
+};
+
+namespace ak {
+
+// One int4 per token row of a step.
+struct RowInfo {
+    int32_t tok_src;  // >= 0 literal id; < 0: -(slot+1) = last sampled token of that slot; INT32_MIN inactive
+    int32_t pos;      // position in its sequence, -1 inactive
+    int32_t slot;     // paged KV slot for the append, -1 none
+    int32_t seq;      // sequence slot the row belongs to
+};
+
+struct StepDesc {  // offsets (in int32 units) into the descriptor buffer
+    uint32_t kv_lens, out_rows, pf_cu, pf_slot, block_tables, rows, total;
+};
+
+class Runner {
+   public:
+    Runner() = default;
+    ~Runner();
+    int init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq_len, uint32_t kv_blocks, uint32_t max_prefill_tokens);
+    // Host mirror of the descriptor (pinned). Fill, then run().
+    int32_t* h_kv_lens() { return h_desc_ + d_.kv_lens; }
+    int32_t* h_out_rows() { return h_desc_ + d_.out_rows; }
+    int32_t* h_pf_cu() { return h_desc_ + d_.pf_cu; }
+    int32_t* h_pf_slot() { return h_desc_ + d_.pf_slot; }
+    int32_t* h_block_table(uint32_t seq) { return h_desc_ + d_.block_tables + (size_t)seq * max_blocks_; }
+    RowInfo* h_rows() { return reinterpret_cast<RowInfo*>(h_desc_ + d_.rows); }
+    const uint32_t* h_sampled() const { return h_sampled_; }
+
+    // Launch one step over rows [0, max_seqs_) (decode rows, one per slot) plus n_prefill_rows
+    // prefill rows. Ends with the sampled tokens copied to the pinned host buffer (async).
+    int run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t max_kv_len);
+    // Decode-only step through a captured CUDA graph (captured on first use).
+    int run_decode_graph(uint32_t max_kv_len_hint);
+    int sync();
+    int read_logits(uint32_t slot, float* host_out);
+    int gather_cache(uint32_t layer, const int32_t* h_table, uint32_t len, float* k_out, float* v_out);
+
+    uint32_t max_seqs() const { return max_seqs_; }
+    uint32_t max_blocks() const { return max_blocks_; }
+    uint32_t n_blocks() const { return n_blocks_; }
+    uint32_t max_prefill_tokens() const { return max_pf_tokens_; }
+    uint32_t dtype() const { return w_->dtype; }
+    void enable_attn_timing(bool on) { attn_timing_ = on; }
+    float last_attn_ms();
+    uint64_t graph_launches = 0, eager_steps = 0;
+
+   private:
+    int launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t n_splits, bool capturing);
+    int gemm(const void* a, const void* w, void* c, uint32_t m, uint32_t n, uint32_t k, int mode);
+
+    ak_ctx* ctx_ = nullptr;
+    ak_weights* w_ = nullptr;
+    uint32_t max_seqs_ = 0, max_blocks_ = 0, n_blocks_ = 0, max_pf_tokens_ = 0, max_rows_ = 0, max_seq_len_ = 0;
+    StepDesc d_{};
+    int32_t* h_desc_ = nullptr;  // pinned
+    int32_t* d_desc_ = nullptr;
+    uint32_t* h_sampled_ = nullptr;  // pinned
+    uint32_t* d_sampled_ = nullptr;
+    std::vector<void*> k_pool_, v_pool_;
+    float* hidden_ = nullptr;
+    void* xn_ = nullptr;
+    float* qkv_ = nullptr;
+    void* qbuf_ = nullptr;
+    void* attn_ = nullptr;
+    void* up_ = nullptr;
+    void* xf_ = nullptr;
+    float* logits_ = nullptr;
+    float* attn_scratch_ = nullptr;
+    size_t attn_scratch_bytes_ = 0;
+    float2* rope_table_ = nullptr;
+    uint32_t rope_len_ = 0;
+    cudaGraphExec_t graph_exec_ = nullptr;
+    uint32_t graph_splits_ = 0;
+    bool attn_timing_ = false;
+    cudaEvent_t ev_attn0_ = nullptr, ev_attn1_ = nullptr;
+    bool ev_valid_ = false;
+};
+
+}  // namespace ak

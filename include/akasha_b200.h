@@ -1,0 +1,305 @@
+/*
+ * akasha_b200.h -- C ABI of the B200 (sm_100a) backend for the akasha-hall Prefill/Decode
+ * inference path.
+ *
+ * Three levels, all `extern "C"`, plain pointers and sizes only:
+ *   1. emitter level  -- one entry point per forward/cached kernel emitter of the reference's
+ *                        `src/nn/ops/emit.rs`, taking DEVICE pointers and the same `#[repr(C)]`
+ *                        meta struct (by value) that `src/nn/ops/meta.rs` defines; plus the new
+ *                        fused B200 kernels (paged decode attention, tcgen05 GEMM, ...).
+ *   2. session level  -- mirrors `InferenceSession` (src/nn/inference.rs:13-327).
+ *   3. engine level   -- continuous batching over a paged KV cache (new: the reference has no
+ *                        batching, ARCHITECTURE.md:376-377).
+ *
+ * Every function returns an `ak_status`; 0 is success. Codes 1..5 mirror `AkashaError`
+ * (src/lib.rs:10-17) in declaration order. Nothing here aborts the process, and no device code
+ * traps: device-side waits are bounded and report through a status word.
+ *
+ * `stream` arguments are a `cudaStream_t` passed as `void*` (NULL = the default stream).
+ * No handle is thread-safe; calls on one handle must be serialised by the caller
+ * (the reference API is `&mut self`, src/nn/inference.rs:61,178).
+ */
+#ifndef AKASHA_B200_H
+#define AKASHA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AK_API __attribute__((visibility("default")))
+#else
+#define AK_API
+#endif
+
+/* ------------------------------------------------------------------ status */
+typedef enum ak_status {
+    AK_OK = 0,
+    AK_EMPTY_PROMPT = 1,    /* AkashaError::EmptyPrompt    (src/lib.rs:12) */
+    AK_PROMPT_TOO_LONG = 2, /* AkashaError::PromptTooLong  (src/lib.rs:13) */
+    AK_CONTEXT_FULL = 3,    /* AkashaError::ContextFull    (src/lib.rs:14) */
+    AK_NO_CACHE = 4,        /* AkashaError::NoCache        (src/lib.rs:15) */
+    AK_CACHE_NOT_EMPTY = 5, /* AkashaError::CacheNotEmpty  (src/lib.rs:16) */
+    AK_ERR_INVALID_ARG = 100,
+    AK_ERR_CUDA = 101,
+    AK_ERR_ALLOC = 102,
+    AK_ERR_UNSUPPORTED = 103, /* shape / dtype the sm_100a kernels do not cover */
+    AK_ERR_DEVICE_WAIT = 104, /* a bounded device-side wait ran out (status word set) */
+    AK_ERR_NO_CAPACITY = 105, /* engine: no free sequence slot or KV block */
+    AK_ERR_NOT_FOUND = 106
+} ak_status;
+
+/* Text of the last error raised on the calling thread ("" if none). */
+AK_API const char* ak_last_error_string(void);
+/* Library version string, and the compute architecture the kernels were built for. */
+AK_API const char* ak_version(void);
+/* Kernel launches issued by this library on the calling thread since it loaded. */
+AK_API unsigned long long ak_launch_count(void);
+/* Synchronise `stream` and read the device status words: AK_ERR_DEVICE_WAIT if a bounded
+ * device-side wait (mbarrier / TMA / tcgen05 pipeline) ever ran out, AK_OK otherwise. */
+AK_API int ak_check_device_status(void* stream);
+
+/* ------------------------------------------------------------------ dtypes */
+typedef enum ak_dtype {
+    AK_F32 = 0, /* fp32 weights, KV and activations: the parity mode (true fp32 FMA everywhere) */
+    AK_BF16 = 1 /* bf16 weights / KV / activations, fp32 accumulate and fp32 residual stream */
+} ak_dtype;
+
+/* ------------------------------------------------------------------ model config
+ * ModelConfig (src/config.rs:2-30). ffn_hidden = 4*dim, norm_eps = 1e-5 and
+ * eos_token = vocab_size-1 are what `ModelConfig::new` fixes; they are explicit fields here. */
+typedef struct ak_model_config {
+    uint32_t vocab_size;
+    uint32_t dim;
+    uint32_t num_heads;
+    uint32_t num_layers;
+    uint32_t seq_len; /* the model's nominal context (informational) */
+    uint32_t ffn_hidden;
+    float norm_eps;
+    uint32_t eos_token;
+} ak_model_config;
+
+/* ------------------------------------------------------------------ typed kernel metas
+ * Field-for-field the `#[repr(C)]` structs of src/nn/ops/meta.rs (all members 4 bytes). */
+typedef struct ak_matmul_meta { uint32_t m, n, k; } ak_matmul_meta;                     /* meta.rs:19-25  */
+typedef struct ak_norm_meta { uint32_t seq_len, size; float eps; } ak_norm_meta;        /* meta.rs:29-35  */
+typedef struct ak_head_move_meta { uint32_t seq_len, full_dim, head_dim, head_offset; } ak_head_move_meta; /* meta.rs:40-47 */
+typedef struct ak_attn_cached_meta { uint32_t attn_len, dim, head_dim; } ak_attn_cached_meta; /* meta.rs:62-68 */
+typedef struct ak_softmax_rect_meta { uint32_t num_rows, width; float scale; } ak_softmax_rect_meta; /* meta.rs:72-78 */
+typedef struct ak_rope_meta { uint32_t seq_len, dim, head_dim, row_offset; } ak_rope_meta; /* meta.rs:82-89 */
+typedef struct ak_rope_offset_meta { uint32_t seq_len, dim, head_dim, pos; } ak_rope_offset_meta; /* meta.rs:93-100 */
+typedef struct ak_cache_write_meta { uint32_t row_count, width, dst_row_offset; } ak_cache_write_meta; /* meta.rs:104-110 */
+typedef struct ak_embedding_meta { uint32_t vocab_size, dim, seq_len; } ak_embedding_meta; /* meta.rs:114-120 */
+typedef struct ak_flash_attn_meta { uint32_t seq_len, dim, head_dim; float scale; uint32_t row_offset; } ak_flash_attn_meta; /* meta.rs:156-164 */
+
+/* ------------------------------------------------------------------ device helpers
+ * For hosts that have no CUDA runtime binding of their own (the reference's Tensor::
+ * init_from_cpu / copy_from_cpu / to_cpu, used at src/nn/inference.rs:83,189,261). */
+AK_API int ak_device_count(int* out);
+AK_API int ak_set_device(int device);
+AK_API int ak_device_malloc(void** out, size_t bytes);
+AK_API int ak_device_free(void* p);
+AK_API int ak_memcpy_h2d(void* dst, const void* src, size_t bytes, void* stream);
+AK_API int ak_memcpy_d2h(void* dst, const void* src, size_t bytes, void* stream);
+AK_API int ak_memset(void* dst, int value, size_t bytes, void* stream);
+AK_API int ak_stream_create(void** out);
+AK_API int ak_stream_destroy(void* stream);
+AK_API int ak_stream_synchronize(void* stream); /* ctx.synchronize(), src/nn/ops/emit.rs:1052 */
+AK_API int ak_host_alloc_pinned(void** out, size_t bytes);
+AK_API int ak_host_free_pinned(void* p);
+
+/* ================================================================== 1. emitter level
+ * All pointers are device pointers; f32 row-major as in the reference. Output-mode buffers are
+ * fully overwritten, Accumulate-mode buffers are `+=` (ARCHITECTURE.md:226-231). */
+
+/* ops::embedding (src/nn/ops/emit.rs:228-257; kernel src/shaders/cuda.rs:5-31):
+ * out[t,:] = table[tokens[t],:], a zero row for an id >= vocab_size. */
+AK_API int ak_embedding(void* stream, const uint32_t* tokens, const float* table, float* out, ak_embedding_meta m);
+/* ops::rmsnorm (emit.rs:151-180; cuda.rs:421-456): y = x * rsqrt(mean(x^2)+eps) * w per row. */
+AK_API int ak_rmsnorm(void* stream, const float* x, const float* w, float* y, ak_norm_meta m);
+/* ops::matmul (emit.rs:23-57): C[m,n] = A[m,k] @ B[k,n]; m == 1 routes to the GEMV kernel. */
+AK_API int ak_matmul(void* stream, const float* a, const float* b, float* c, ak_matmul_meta m);
+/* ops::matmul_add (emit.rs:92-126): C[m,n] += A[m,k] @ B[k,n] (fused residual). */
+AK_API int ak_matmul_add(void* stream, const float* a, const float* b, float* c, ak_matmul_meta m);
+/* ops::head_gather (emit.rs:406-424; cuda.rs:256-274): dst[r,c] = src[r*full_dim+head_offset+c]. */
+AK_API int ak_head_gather(void* stream, const float* src, float* dst, ak_head_move_meta m);
+/* ops::rope (emit.rs:306-313; cuda.rs:98-123): in-place, adjacent pairs, position = row index. */
+AK_API int ak_rope(void* stream, float* x, ak_rope_meta m);
+/* ops::rope_offset_with (emit.rs:325-342; cuda.rs:224-254): position = row index + pos. */
+AK_API int ak_rope_offset(void* stream, float* x, ak_rope_offset_meta m);
+/* ops::cache_write (emit.rs:649-675; cuda.rs:614-631): cache[(off+r)*width+c] = src[r*width+c]. */
+AK_API int ak_cache_write(void* stream, const float* src, float* cache, ak_cache_write_meta m);
+/* ops::attn_qk_cached_with (emit.rs:485-504; cuda.rs:349-369): scores[h*attn_len+j] = q_h . K[j]_h (unscaled). */
+AK_API int ak_attn_qk_cached(void* stream, const float* q, const float* k_cache, float* scores, ak_attn_cached_meta m);
+/* ops::softmax_rect_with (emit.rs:528-542; cuda.rs:391-419): rows of softmax(scale*x), in place. */
+AK_API int ak_softmax_rect(void* stream, float* x, ak_softmax_rect_meta m);
+/* ops::attn_av_cached_with (emit.rs:507-525; cuda.rs:371-389): out[d] = sum_j P[d/hd, j] * V[j, d]. */
+AK_API int ak_attn_av_cached(void* stream, const float* scores, const float* v_cache, float* out, ak_attn_cached_meta m);
+/* ops::flash_attention (emit.rs:556-597; cuda.rs:633-685): causal attention over rows
+ * row_offset..row_offset+seq_len of q/k/v [*, dim]; l_cache (may be NULL) = max + log(sum). */
+AK_API int ak_flash_attention(void* stream, const float* q, const float* k, const float* v, float* out, float* l_cache, ak_flash_attn_meta m);
+/* ops::silu (emit.rs:686-696; cuda.rs:57-65): x = x / (1 + exp(-x)) in place, any n < 2^32. */
+AK_API int ak_silu(void* stream, float* x, uint32_t n);
+/* sampling::argmax (src/nn/sampling.rs:83-91) on the device: for each of `rows` rows of `n`
+ * logits the FIRST index holding the maximum. out_idx: device uint32[rows]. */
+AK_API int ak_argmax(void* stream, const float* logits, uint32_t rows, uint32_t n, uint32_t* out_idx);
+
+/* ---- new fused sm_100a kernels (no single-emitter counterpart in the reference) ---- */
+
+/* Ragged paged decode attention: fuses attn_qk_cached + softmax_rect + attn_av_cached
+ * (src/nn/inference_graphs.rs:428-456) for `rows` independent sequences in one launch.
+ *   q, out      [rows, heads*head_dim]      (kv_dtype: f32 or bf16, same type for q/out/pools)
+ *   k_pool/v_pool  [n_blocks, heads, block_size(16), head_dim]
+ *   block_tables   int32 [rows, max_blocks_per_seq]; kv_lens int32 [rows] (0 = row skipped,
+ *                  its output is zero-filled)
+ *   slot(pos) = block_tables[row][pos/16]*16 + pos%16
+ *   scratch: device buffer of ak_attn_decode_scratch_bytes() bytes, needed only when the
+ *            launch splits sequences over several CTAs (n_splits > 1); may be NULL otherwise.
+ *   n_splits: 0 = let the library choose. */
+typedef struct ak_attn_decode_params {
+    uint32_t rows, heads, head_dim, block_size, max_blocks_per_seq;
+    float scale;
+    uint32_t kv_dtype; /* ak_dtype */
+    uint32_t n_splits;
+    uint32_t pool_blocks; /* blocks in each pool; 0 = unknown (no range protection) */
+} ak_attn_decode_params;
+AK_API size_t ak_attn_decode_scratch_bytes(const ak_attn_decode_params* p);
+AK_API int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool, const void* v_pool,
+                                const int32_t* block_tables, const int32_t* kv_lens, void* out,
+                                void* scratch, ak_attn_decode_params p);
+
+/* Fused head split + RoPE + paged KV append (head_gather x3, rope(_offset) x2, cache_write x2:
+ * src/nn/inference_graphs.rs:241-269, 385-426) over a ragged token batch.
+ *   qkv [tokens, 3*dim] f32;  positions int32[tokens];  slots int32[tokens] (paged slot of the
+ *   token, -1 = do not append);  q_out [tokens, dim];  pools as above (dtype = kv_dtype).
+ * K is stored after RoPE, V raw (ARCHITECTURE.md:256-280). 128-bit stores throughout. */
+AK_API int ak_rope_kv_append(void* stream, const float* qkv, const int32_t* positions, const int32_t* slots,
+                             void* q_out, void* k_pool, void* v_pool, uint32_t tokens, uint32_t heads,
+                             uint32_t head_dim, uint32_t block_size, uint32_t kv_dtype);
+
+/* One kernel: h = x (+ residual, written back to x when given), y = rmsnorm(h) * w, then an
+ * optional RoPE of y (adjacent pairs per head, positions[row]; head_dim = 0 disables).
+ * y is f32 or bf16 (out_dtype). */
+AK_API int ak_rmsnorm_rope_residual(void* stream, float* x, const float* residual, const float* w, void* y,
+                                    const int32_t* positions, uint32_t rows, uint32_t size, float eps,
+                                    uint32_t head_dim, uint32_t out_dtype);
+
+/* bf16 tensor-core GEMM (tcgen05.mma, TMEM accumulator, TMA-staged operands):
+ *   C[m,n] (op)= A[m,k] @ Wt[n,k]^T,  A bf16 row-major, Wt bf16 row-major (the TRANSPOSE of the
+ *   reference's [k,n] weight, made once at upload), fp32 accumulate.
+ * epilogue: see ak_gemm_epilogue. k must be a multiple of 8 (16-byte rows). */
+typedef enum ak_gemm_epilogue {
+    AK_EPI_STORE_F32 = 0,  /* C f32 = acc                     (matmul)            */
+    AK_EPI_ADD_F32 = 1,    /* C f32 += acc                    (matmul_add)        */
+    AK_EPI_STORE_BF16 = 2, /* C bf16 = acc                                        */
+    AK_EPI_SILU_BF16 = 3   /* C bf16 = silu(acc)              (matmul + silu)     */
+} ak_gemm_epilogue;
+AK_API int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue);
+/* Make the [n,k] bf16 operand from a reference-layout f32 [k,n] matrix (device to device). */
+AK_API int ak_transpose_to_bf16(void* stream, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);
+AK_API int ak_f32_to_bf16(void* stream, const float* src, void* dst, uint64_t n);
+AK_API int ak_bf16_to_f32(void* stream, const void* src, float* dst, uint64_t n);
+
+/* ================================================================== 2. session level */
+typedef struct ak_ctx ak_ctx;         /* one device + one stream (Arc<B: Backend>) */
+typedef struct ak_weights ak_weights; /* ModelWeights (src/nn/weights.rs:40-47)     */
+typedef struct ak_session ak_session; /* InferenceSession (src/nn/inference.rs:13)  */
+
+AK_API int ak_ctx_create(int device, ak_ctx** out); /* CudaBackend::new(device), src/main.rs:366 */
+AK_API int ak_ctx_destroy(ak_ctx* ctx);
+AK_API int ak_ctx_synchronize(ak_ctx* ctx);
+AK_API void* ak_ctx_stream(ak_ctx* ctx);
+
+/* ModelWeights::zeros (src/nn/weights.rs:124-156): allocate all tensors, zero-filled. */
+AK_API int ak_weights_create(ak_ctx* ctx, const ak_model_config* cfg, uint32_t dtype, ak_weights** out);
+AK_API int ak_weights_destroy(ak_weights* w);
+/* Number of tensors (1 + 6*layers + 2) and element count of tensor `index`, in
+ * `ModelWeights::params()` order (src/nn/weights.rs:158-171): embedding, per block
+ * {norm_1, qkv_proj, out_proj, norm_2, ffn_up, ffn_down}, final_norm, lm_head. */
+AK_API uint32_t ak_weights_param_count(const ak_weights* w);
+AK_API uint64_t ak_weights_param_len(const ak_weights* w, uint32_t index);
+/* Tensor::copy_from_cpu per parameter (src/nn/checkpoint.rs:98-161 loads in this order).
+ * `host` is f32 in the reference layout (matrices [in,out] row-major); the library converts to
+ * its device layout (bf16 mode: cast, projection matrices stored transposed). */
+AK_API int ak_weights_set_param(ak_weights* w, uint32_t index, const float* host, uint64_t n_elems);
+/* Read a parameter back as f32 in the reference layout (bf16 mode returns the rounded values). */
+AK_API int ak_weights_get_param(ak_weights* w, uint32_t index, float* host, uint64_t n_elems);
+/* Fill every tensor on the device from a counter-based generator: matrices ~ N(0, std),
+ * norm gains ~ N(1, std). Deterministic in (seed, index, element). For benchmarks. */
+AK_API int ak_weights_init_synthetic(ak_weights* w, uint64_t seed, float std);
+
+/* InferenceSession::new (src/nn/inference.rs:25-40). The cache is created with the session
+ * but DETACHED, as in the reference (`cache: None`): prefill returns AK_NO_CACHE until
+ * ak_session_attach_cache or ak_session_generate_greedy attaches it. */
+AK_API int ak_session_create(ak_ctx* ctx, ak_weights* w, uint32_t max_context_len, ak_session** out);
+AK_API int ak_session_destroy(ak_session* s);
+/* replace_cache(Cache::new(..)) (src/nn/inference.rs:42-54): attach an empty cache. */
+AK_API int ak_session_attach_cache(ak_session* s);
+/* take_cache (src/nn/inference.rs:56-59): detach; the next prefill needs a new attach. */
+AK_API int ak_session_take_cache(ak_session* s);
+/* Cache::reset (src/nn/inference_graphs.rs:540-542): cur_len = 0, memory untouched. */
+AK_API int ak_session_reset_cache(ak_session* s);
+AK_API uint32_t ak_session_cur_len(const ak_session* s);
+/* prefill (src/nn/inference.rs:61-176). logits_out: host f32[vocab] or NULL;
+ * argmax_out: host uint32 or NULL (greedy token of the returned logits, computed on device). */
+AK_API int ak_session_prefill(ak_session* s, const uint32_t* tokens, uint32_t n, float* logits_out, uint32_t* argmax_out);
+/* decode_step (src/nn/inference.rs:178-262). */
+AK_API int ak_session_decode_step(ak_session* s, uint32_t token, float* logits_out, uint32_t* argmax_out);
+/* generate (src/nn/inference.rs:264-326) with temperature <= 0 and repetition_penalty == 1
+ * (greedy, src/nn/sampling.rs:30-32): attaches a cache if none, prefill when the cache is empty
+ * else decode_step over the prompt, then up to max_new tokens; stops after emitting `eos` when
+ * stop_on_eos != 0, and stops quietly when the context fills. Token ids only cross PCIe. */
+AK_API int ak_session_generate_greedy(ak_session* s, const uint32_t* prompt, uint32_t n, uint32_t max_new,
+                                      int stop_on_eos, uint32_t* out_tokens, uint32_t* n_out);
+/* Copy the cached K (post-RoPE) and V rows 0..cur_len-1 of one layer to host as f32
+ * [cur_len, dim] in the reference's contiguous layout (src/nn/inference_graphs.rs:511-543). */
+AK_API int ak_session_read_cache(ak_session* s, uint32_t layer, float* k_out, float* v_out);
+
+/* ================================================================== 3. engine level
+ * Continuous batching: up to max_seqs sequences decode together, one launch per layer-op over
+ * the ragged batch; a finished sequence's slot and KV blocks are reused by the next waiting one.
+ * Block allocation is deterministic: lowest free block index first; a finished sequence's
+ * blocks are returned before the next admission. */
+typedef struct ak_engine ak_engine;
+typedef struct ak_engine_config {
+    uint32_t max_seqs;         /* concurrent sequences (64 in the headline config) */
+    uint32_t max_seq_len;      /* longest prompt+generation of one sequence         */
+    uint32_t kv_blocks;        /* KV pool size in blocks (0 = max_seqs * ceil(max_seq_len/16)) */
+    uint32_t block_size;       /* must be 16 */
+    uint32_t max_batch_tokens; /* token budget of one step (prefill + decode rows)  */
+    uint32_t use_cuda_graph;   /* capture the decode-only step in a CUDA graph      */
+    uint32_t stop_on_eos;      /* 0: run every sequence to its max_len              */
+    uint32_t attn_timing;      /* record CUDA events around layer 0's decode attention */
+} ak_engine_config;
+
+AK_API int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak_engine** out);
+AK_API int ak_engine_destroy(ak_engine* e);
+/* Queue a sequence: it generates until its total length reaches max_total_len (or eos). */
+AK_API int ak_engine_submit(ak_engine* e, const uint32_t* prompt, uint32_t n, uint32_t max_total_len, uint64_t* seq_id);
+/* One scheduler step: admit waiting sequences into free slots (their prompts are prefilled in
+ * this step's ragged batch), run one token for every running sequence, retire finished ones.
+ * n_running / n_finished_total may be NULL. Returns after the step's token ids are on the host. */
+AK_API int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting);
+/* Has the sequence finished? Its generated tokens (prompt excluded) are copied to out (capacity
+ * cap); n_out gets the count generated so far. */
+AK_API int ak_engine_poll(ak_engine* e, uint64_t seq_id, uint32_t* out, uint32_t cap, uint32_t* n_out, int* finished);
+/* Block table of a live or finished sequence (int32 block ids, in position order). */
+AK_API int ak_engine_block_table(ak_engine* e, uint64_t seq_id, int32_t* out, uint32_t cap, uint32_t* n_out);
+/* Forget finished sequences' records. */
+AK_API int ak_engine_clear_finished(ak_engine* e);
+typedef struct ak_engine_stats {
+    uint64_t steps, decode_tokens, prefill_tokens, graph_launches, eager_steps, kernel_launches;
+    double attn_ms_total;        /* sum of timed layer-0 decode-attention launches (attn_timing) */
+    uint64_t attn_launches_timed;
+    uint64_t attn_bytes_total;   /* algorithmic bytes of those launches */
+} ak_engine_stats;
+AK_API int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out);
+AK_API int ak_engine_reset_stats(ak_engine* e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AKASHA_B200_H */
