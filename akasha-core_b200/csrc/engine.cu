@@ -66,7 +66,13 @@ int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak
     e->cfg.block_size = 16;
     const uint32_t mb = (cfg->max_seq_len + 15) / 16;
     if (e->cfg.kv_blocks == 0) e->cfg.kv_blocks = cfg->max_seqs * mb;
-    if (e->cfg.max_batch_tokens < cfg->max_seqs + 1) e->cfg.max_batch_tokens = cfg->max_seqs + cfg->max_seq_len;
+    if (e->cfg.max_batch_tokens < cfg->max_seqs + 1) {
+        // default step budget: every slot may be (re)filled in one step, capped at 32k prompt rows
+        uint64_t pf = (uint64_t)cfg->max_seqs * cfg->max_seq_len;
+        if (pf > 32768) pf = 32768;
+        if (pf < cfg->max_seq_len) pf = cfg->max_seq_len;
+        e->cfg.max_batch_tokens = cfg->max_seqs + (uint32_t)pf;
+    }
     int rc = e->runner.init(ctx, w, cfg->max_seqs, cfg->max_seq_len, e->cfg.kv_blocks, e->cfg.max_batch_tokens - cfg->max_seqs);
     if (rc) {
         delete e;
@@ -221,6 +227,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     e->stats.prefill_tokens += pf_rows;
     if (graph) e->stats.graph_launches++; else e->stats.eager_steps++;
     e->stats.kernel_launches += (g_launch_count - launches0);
+    e->stats.h2d_bytes = r.h2d_bytes;
+    e->stats.d2h_bytes = r.d2h_bytes;
     if (e->cfg.attn_timing && any_decode) {
         float ms = r.last_attn_ms();
         if (ms > 0.0f) {

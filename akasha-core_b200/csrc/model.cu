@@ -342,6 +342,8 @@ int Runner::run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len
     if (rc) return rc;
     AK_CUDA(cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st));
     eager_steps++;
+    h2d_bytes += bytes;
+    d2h_bytes += (size_t)max_seqs_ * 4;
     return AK_OK;
 }
 
@@ -362,7 +364,10 @@ int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
         AK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         const size_t bytes = ((size_t)d_.rows + (size_t)max_seqs_ * 4) * 4;
         cudaError_t e = cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st);
+        const unsigned long long l0 = g_launch_count;
         rc = (e == cudaSuccess) ? launch_layers(max_seqs_, 0, 0, 0, true, graph_splits_, true) : AK_ERR_CUDA;
+        graph_kernels = g_launch_count - l0;
+        g_launch_count = l0;  // recorded into the graph, not launched
         if (rc == AK_OK) e = cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st);
         cudaError_t e2 = cudaStreamEndCapture(st, &graph);
         if (rc) return rc;
@@ -375,6 +380,9 @@ int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
     }
     AK_CUDA(cudaGraphLaunch(graph_exec_, st));
     graph_launches++;
+    g_launch_count += graph_kernels;
+    h2d_bytes += ((size_t)d_.rows + (size_t)max_seqs_ * 4) * 4;
+    d2h_bytes += (size_t)max_seqs_ * 4;
     return AK_OK;
 }
 

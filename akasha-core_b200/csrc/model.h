@@ -87,6 +87,8 @@ class Runner {
     void enable_attn_timing(bool on) { attn_timing_ = on; }
     float last_attn_ms();
     uint64_t graph_launches = 0, eager_steps = 0;
+    uint64_t h2d_bytes = 0, d2h_bytes = 0;   // bytes copied by run() / run_decode_graph()
+    uint64_t graph_kernels = 0;              // kernel launches recorded in the captured decode step
 
    private:
     int launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t n_splits, bool capturing);

@@ -295,6 +295,7 @@ typedef struct ak_engine_stats {
     double attn_ms_total;        /* sum of timed layer-0 decode-attention launches (attn_timing) */
     uint64_t attn_launches_timed;
     uint64_t attn_bytes_total;   /* algorithmic bytes of those launches */
+    uint64_t h2d_bytes, d2h_bytes; /* bytes the engine copied host->device / device->host */
 } ak_engine_stats;
 AK_API int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out);
 AK_API int ak_engine_reset_stats(ak_engine* e);

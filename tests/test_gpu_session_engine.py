@@ -1,0 +1,300 @@
+"""GPU: session level (InferenceSession mirror) and engine level (continuous batching) against
+the oracle. fp32 parity mode: greedy token ids and KV slot contents bit-exact / logits within
+2e-2 max-abs (the tolerance the task's north star states); bf16 mode: agreement with the oracle's
+bf16-emulating mode and batch invariance."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+LOGIT_TOL = 2e-2
+
+
+def make(ak, ctx, cfg, seed, std, dtype=0):
+    params = ak.synthetic_weights(cfg, seed=seed, std=std)
+    return params, ak.ModelWeights.from_params(ctx, cfg, params, dtype)
+
+
+# ---- src/nn/inference.rs:334-359 ----------------------------------------------------------------
+def test_prefill_logits_match_sequential_decode(ak, orc, ctx):
+    cfg = ak.ModelConfig(97, 32, 4, 2, 16)   # head_dim 8: the generic attention kernels
+    params, w = make(ak, ctx, cfg, 42, 0.15)
+    prompt = np.array([3, 41, 7, 96, 0, 25], np.uint32)
+    s = ak.InferenceSession(ctx, w, 16)
+    s.replace_cache()
+    pl, _ = s.prefill(prompt)
+    assert pl.shape == (97,)
+    s2 = ak.InferenceSession(ctx, w, 16)
+    s2.replace_cache()
+    for t in prompt:
+        dl, _ = s2.decode_step(int(t))
+    assert np.max(np.abs(pl - dl)) < 1e-3
+    om = orc.Model(cfg.as_dict(), params)
+    os_ = orc.Session(om, 16)
+    rc, ol = os_.prefill(prompt)
+    assert np.max(np.abs(pl - ol)) < 1e-4
+    s.close(); s2.close(); w.close()
+
+
+# ---- src/bin/diagnose.rs:675-743 (CHECK 9) -----------------------------------------------------
+def test_kv_cache_decode_equals_naive_forward(ak, orc, ctx):
+    cfg = ak.ModelConfig(64, 64, 4, 2, 16)
+    params, w = make(ak, ctx, cfg, 7, 0.1)
+    full = ak.uniform_tokens(14, 64, seed=3)
+    s = ak.InferenceSession(ctx, w, 16)
+    s.replace_cache()
+    cached = [s.prefill(full[:4])[0]]
+    for t in full[4:-1]:
+        cached.append(s.decode_step(int(t))[0])
+    naive = ak.InferenceSession(ctx, w, 16)
+    for i, cur in enumerate(range(4, 14)):
+        naive.replace_cache()
+        nl, _ = naive.prefill(full[:cur])
+        assert np.max(np.abs(nl - cached[i])) < 1e-3
+    s.close(); naive.close(); w.close()
+
+
+def test_session_error_contract(ak, ctx):
+    """AkashaError mapping (src/lib.rs:10-17; src/nn/inference.rs:62-75, 179-185)."""
+    cfg = ak.ModelConfig(50, 16, 2, 1, 8)
+    _, w = make(ak, ctx, cfg, 1, 0.1)
+    s = ak.InferenceSession(ctx, w, 4)
+
+    def code(fn):
+        with pytest.raises(ak.AkashaError) as e:
+            fn()
+        return e.value.kind
+
+    assert code(lambda: s.prefill([1, 2])) == "NoCache"
+    assert code(lambda: s.decode_step(1)) == "NoCache"
+    s.replace_cache()
+    assert code(lambda: s.prefill([])) == "EmptyPrompt"
+    assert code(lambda: s.prefill([1, 2, 3, 4, 5])) == "PromptTooLong"
+    s.prefill([1, 2, 3, 4])
+    assert code(lambda: s.prefill([1])) == "CacheNotEmpty"
+    assert code(lambda: s.decode_step(1)) == "ContextFull"
+    s.reset_cache()
+    assert s.cur_len == 0
+    s.decode_step(1)
+    assert s.cur_len == 1
+    s.take_cache()
+    assert code(lambda: s.decode_step(1)) == "NoCache"
+    # generate attaches a cache itself and stops quietly when the context fills
+    out = s.generate([1, 2], 10, stop_on_eos=False)
+    assert len(out) == 3 and s.cur_len == 4   # 2 prompt + decode of 2 generated tokens fills ctx 4
+    s.close(); w.close()
+
+
+@pytest.mark.parametrize("cfg_args,prompt_len,steps,max_ctx,std", [
+    ((1024, 128, 2, 2, 64), 9, 24, 64, 0.05),        # head_dim 64: TMA decode kernel, one block..two
+    ((777, 256, 2, 3, 256), 70, 60, 160, 0.04),      # head_dim 128, prompt spans several tiles
+    ((500, 192, 3, 2, 512), 130, 40, 512, 0.05),     # split-KV active (max_ctx 512)
+])
+def test_session_parity_fp32(ak, orc, ctx, cfg_args, prompt_len, steps, max_ctx, std):
+    cfg = ak.ModelConfig(*cfg_args)
+    params, w = make(ak, ctx, cfg, 0, std)
+    prompt = ak.uniform_tokens(prompt_len, cfg.vocab_size, seed=1)
+    s = ak.InferenceSession(ctx, w, max_ctx)
+    s.replace_cache()
+    logits, tok = s.prefill(prompt)
+    toks, all_logits = [tok], [logits]
+    for _ in range(steps - 1):
+        logits, tok = s.decode_step(toks[-1])
+        toks.append(tok)
+        all_logits.append(logits)
+    om = orc.Model(cfg.as_dict(), params)
+    os_ = orc.Session(om, max_ctx)
+    st, want, ol = os_.generate_greedy(prompt, steps, want_logits=True)
+    assert st == 0
+    errs = [float(np.max(np.abs(a - b))) for a, b in zip(all_logits, ol)]
+    assert list(want) == toks, f"tokens diverge at {next(i for i, (a, b) in enumerate(zip(want, toks)) if a != b)}"
+    assert max(errs) < LOGIT_TOL
+    assert max(errs) < 1e-3   # fp32 FMA path: far inside the stated tolerance
+    # device argmax == host argmax of the returned logits (first maximum)
+    assert all(int(np.argmax(l)) == t for l, t in zip(all_logits, toks))
+    # KV slot contents: K rows post-RoPE, V rows raw, position p in row p
+    n = s.cur_len
+    assert n == prompt_len + steps - 1
+    for layer in range(cfg.num_layers):
+        gk, gv = s.read_cache(layer)
+        ok, ov = os_.cache(layer)
+        assert gk.shape == (n, cfg.dim)
+        assert np.max(np.abs(gk - ok[:n])) < 1e-3 and np.max(np.abs(gv - ov[:n])) < 1e-3
+    # generate() (device-fed tokens) reproduces the same ids
+    s.take_cache()
+    gen = s.generate(prompt, steps, stop_on_eos=False)
+    assert gen.tolist() == toks
+    s.close(); w.close()
+
+
+def test_generate_stops_on_eos(ak, orc, ctx):
+    cfg = ak.ModelConfig(16, 64, 1, 1, 64)   # tiny vocab: greedy soon emits eos = 15
+    params, w = make(ak, ctx, cfg, 3, 0.3)
+    om = orc.Model(cfg.as_dict(), params)
+    found = None
+    for seed in range(40):
+        prompt = ak.uniform_tokens(5, 15, seed=seed)
+        st, toks, _ = orc.Session(om, 64).generate_greedy(prompt, 20)
+        hits = np.nonzero(toks == 15)[0]
+        if len(hits) and hits[0] > 0:
+            found = (prompt, toks, int(hits[0]))
+            break
+    assert found, "no seed produced an eos; widen the search"
+    prompt, toks, first = found
+    s = ak.InferenceSession(ctx, w, 64)
+    out = s.generate(prompt, 20, stop_on_eos=True)
+    assert out.tolist() == toks[:first + 1].tolist() and out[-1] == cfg.eos_token
+    s.close(); w.close()
+
+
+def test_weights_roundtrip_and_layout(ak, ctx):
+    cfg = ak.ModelConfig(97, 32, 4, 2, 16)
+    params = ak.synthetic_weights(cfg, seed=9, std=0.1)
+    w = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_F32)
+    back = w.params()
+    assert all(np.array_equal(a, b) for a, b in zip(params, back))
+    w.close()
+    wb = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_BF16)
+    backb = wb.params()
+    import torch
+    for a, b in zip(params, backb):
+        if a.ndim == 1:
+            assert np.array_equal(a, b)          # gains stay f32
+        else:
+            assert np.array_equal(torch.from_numpy(a).bfloat16().float().numpy(), b)  # cast once, layout restored
+    wb.close()
+
+
+# ---- the 162M config-1 case: prompt 64, 128 greedy steps, tokens exact, logits <= 2e-2 --------------
+def test_akasha_hall_config1_parity(ak, orc, ctx):
+    cfg = ak.ModelConfig.akasha_hall_1()
+    params = ak.synthetic_weights(cfg, seed=0, std=0.02)
+    w = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_F32)
+    prompt = ak.uniform_tokens(64, cfg.vocab_size, seed=1)
+    steps = 128
+    s = ak.InferenceSession(ctx, w, 512)
+    s.replace_cache()
+    logits, tok = s.prefill(prompt)
+    toks, all_logits = [tok], [logits]
+    for _ in range(steps - 1):
+        logits, tok = s.decode_step(toks[-1])
+        toks.append(tok)
+        all_logits.append(logits)
+    om = orc.Model(cfg.as_dict(), params)
+    st, want, ol = orc.Session(om, 512).generate_greedy(prompt, steps, want_logits=True)
+    errs = [float(np.max(np.abs(a - b))) for a, b in zip(all_logits, ol)]
+    margins = []
+    for l in ol[:steps]:
+        top2 = np.partition(l, -2)[-2:]
+        margins.append(float(top2[1] - top2[0]))
+    print(f"config-1: max |dlogit| {max(errs):.3e}, min top-2 margin {min(margins):.3e}")
+    assert list(want) == toks
+    assert max(errs) < LOGIT_TOL
+    s.close(); w.close()
+
+
+# ================================================================================ engine
+def run_engine(ak, ctx, w, prompts, total_len, max_seqs, graph, max_seq_len=None):
+    e = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=max_seq_len or total_len, use_cuda_graph=graph)
+    ids = [e.submit(p, total_len) for p in prompts]
+    steps = e.run_to_completion(100000)
+    outs, tables = [], []
+    for i in ids:
+        t, fin = e.poll(i)
+        assert fin
+        outs.append(t)
+        tables.append(e.block_table(i))
+    st = e.stats()
+    e.close()
+    return outs, tables, st, steps
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_engine_matches_independent_oracle_sessions_fp32(ak, orc, ctx, graph):
+    """The engine's oracle is N independent single-sequence reference sessions: per sequence the
+    generated ids are identical; block tables follow the lowest-free-first rule exactly."""
+    cfg = ak.ModelConfig(600, 128, 2, 2, 96)
+    params, w = make(ak, ctx, cfg, 0, 0.06)
+    total, max_seqs, n = 96, 4, 11
+    lens = ak.uniform_ints(n, 3, 60, seed=2)
+    prompts = [ak.uniform_tokens(int(l), cfg.vocab_size, seed=100 + i) for i, l in enumerate(lens)]
+    outs, tables, st, steps = run_engine(ak, ctx, w, prompts, total, max_seqs, graph)
+    om = orc.Model(cfg.as_dict(), params)
+    for p, o in zip(prompts, outs):
+        stt, want, _ = orc.Session(om, total).generate_greedy(p, total - len(p))
+        assert o.tolist() == want.tolist()
+        assert len(o) == total - len(p)
+    # slot indexing: replay the admission/retire order on the oracle's allocator
+    pool = orc.BlockPool(max_seqs * ((total + 15) // 16))
+    need = (total + 15) // 16
+    finish_step, live, waiting, exp_tables = {}, {}, list(range(n)), {}
+    step = 0
+    while waiting or live:
+        for i in [i for i, f in live.items() if f <= step]:
+            for b in exp_tables[i]:
+                pool.free(int(b))
+            del live[i]
+        while waiting and len(live) < max_seqs:
+            i = waiting.pop(0)
+            exp_tables[i] = [pool.alloc() for _ in range(need)]
+            live[i] = step + (total - len(prompts[i]))   # one token per step, first one in the admit step
+        step += 1
+    for i in range(n):
+        assert tables[i].tolist() == exp_tables[i]
+    assert st["decode_tokens"] + n == sum(len(o) for o in outs)
+    assert st["prefill_tokens"] == sum(len(p) for p in prompts)
+    if graph:
+        assert st["graph_launches"] > 0
+    w.close()
+
+
+def test_engine_bf16_batch_invariance_and_oracle_agreement(ak, orc, ctx):
+    """bf16 mode: a sequence's ids do not depend on what else is in the batch (alone == batched),
+    and they agree with the oracle's bf16-emulating mode except where the top-2 margin is tiny."""
+    cfg = ak.ModelConfig(2000, 256, 4, 3, 128)
+    params = ak.synthetic_weights(cfg, seed=5, std=0.05)
+    w = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_BF16)
+    total, n = 128, 9
+    lens = ak.uniform_ints(n, 5, 90, seed=4)
+    prompts = [ak.uniform_tokens(int(l), cfg.vocab_size, seed=200 + i) for i, l in enumerate(lens)]
+    batched, _, st, _ = run_engine(ak, ctx, w, prompts, total, 4, True)
+    for i in (0, 3, 8):
+        alone, _, _, _ = run_engine(ak, ctx, w, [prompts[i]], total, 4, True)
+        assert alone[0].tolist() == batched[i].tolist()
+    rparams = [p if p.ndim == 1 else orc.round_bf16(p) for p in params]
+    om = orc.Model(cfg.as_dict(), rparams, act_bf16=True)
+    agree = total_tok = 0
+    for p, o in zip(prompts, batched):
+        stt, want, _ = orc.Session(om, total).generate_greedy(p, total - len(p))
+        k = next((j for j, (a, b) in enumerate(zip(want, o)) if a != b), len(o))
+        agree += k
+        total_tok += len(o)
+    print(f"bf16 engine vs bf16-emulating oracle: {agree}/{total_tok} tokens agree before first divergence")
+    assert agree / total_tok > 0.5
+    w.close()
+
+
+def test_engine_capacity_and_errors(ak, ctx):
+    cfg = ak.ModelConfig(100, 64, 1, 1, 64)
+    _, w = make(ak, ctx, cfg, 1, 0.1)
+    e = ak.Engine(ctx, w, max_seqs=2, max_seq_len=48)
+    with pytest.raises(ak.AkashaError) as ei:
+        e.submit([], 10)
+    assert ei.value.kind == "EmptyPrompt"
+    with pytest.raises(ak.AkashaError) as ei:
+        e.submit(list(range(49)), 48)
+    assert ei.value.kind == "PromptTooLong"
+    with pytest.raises(ak.AkashaError) as ei:
+        e.submit([1, 2, 3], 3)
+    assert ei.value.kind == "ContextFull"
+    ids = [e.submit([1, 2, 3], 8 + i) for i in range(5)]
+    r, wq = e.step()
+    assert r == 2 and wq == 3       # two slots, three waiting
+    e.run_to_completion(1000)
+    for k, i in enumerate(ids):
+        t, fin = e.poll(i)
+        assert fin and len(t) == 5 + k
+    e.clear_finished()
+    with pytest.raises(ak.AkashaError):
+        e.poll(ids[0])
+    e.close(); w.close()
