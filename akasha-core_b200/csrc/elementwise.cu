@@ -32,10 +32,12 @@ __global__ void embed_rows_kernel(const int32_t* __restrict__ tok_src, uint32_t 
                                   float* __restrict__ hidden, uint32_t vocab, uint32_t dim) {
     uint32_t r = blockIdx.x;
     int32_t ts = tok_src[(size_t)r * idx_stride];
-    uint32_t id = (ts >= 0) ? (uint32_t)ts : sampled[(uint32_t)(-(ts + 1))];
-    // INT32_MIN marks an inactive row
-    bool ok = (ts != INT32_MIN) && id < vocab;
-    const WT* src = table + (size_t)id * dim;
+    // INT32_MIN marks an inactive row: it must not be decoded as a slot reference
+    const bool active = ts != INT32_MIN;
+    uint32_t id = 0;
+    if (active) id = (ts >= 0) ? (uint32_t)ts : sampled[(uint32_t)(-(ts + 1))];
+    bool ok = active && id < vocab;
+    const WT* src = table + (size_t)(ok ? id : 0) * dim;
     float* dst = hidden + (size_t)r * dim;
     for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? Cvt<WT>::to_f(src[i]) : 0.0f;
 }

@@ -1,0 +1,173 @@
+"""Kernel microbenchmarks (one JSON line per kernel), timed with CUDA events on the launching stream.
+
+    python akasha-core_b200/microbench.py [attn] [gemm] [norm] [engine] [--iters N] [--small]
+
+  attn : ragged paged decode attention, 1024 sequences, 12 heads x 64, KV lengths U[1,512] (seed 3),
+         bf16 K/V ~ N(0,1), block 16.  Reports algorithmic GB/s against the measured HBM peak.
+  gemm : tcgen05 bf16 GEMM, M = 32768, K = 768, N in {2304, 3072, 50257}. Reports TFLOP/s.
+  norm : fused RMSNorm + RoPE (+ residual) on 32768 x 768 rows, f32 in / bf16 out. Reports GB/s.
+  engine : steady-state decode steps of the 162M engine with 64 ragged sequences in flight
+         (not in the default set; the launch sequence to hand to a profiler).
+
+`--small` shrinks every case (for a profiler capture: inputs stay above the 126 MB L2 where it
+matters, a few launches, well under a GB on the device).
+Every input is larger than L2 or the buffers are rotated, so no iteration re-reads a warm cache.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timed(torch, fn, iters, warmup=3):
+    st = torch.cuda.current_stream()
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(st)
+    for _ in range(iters):
+        fn()
+    e1.record(st)
+    e1.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_attn(ak, torch, iters, small):
+    rows, heads, hd, max_blocks = (256 if small else 1024), 12, 64, 32
+    lens = ak.uniform_ints(rows, 1, 512, seed=3)
+    n_blocks = rows * max_blocks
+    g = torch.Generator(device="cuda").manual_seed(3)
+    kp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
+    vp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
+    perm = torch.randperm(n_blocks, device="cuda", generator=g).to(torch.int32).reshape(rows, max_blocks)
+    q = torch.randn(rows, heads * hd, device="cuda", generator=g).bfloat16()
+    out = torch.empty_like(q)
+    kv_lens = torch.from_numpy(lens.astype(np.int32)).cuda()
+    stream = torch.cuda.current_stream().cuda_stream
+    fn = lambda: ak.ops.attn_decode_paged(q, kp, vp, perm, kv_lens, out, rows, heads, hd, max_blocks, 0.125,
+                                          ak.AK_BF16, 1, n_blocks, None, stream)
+    ms = timed(torch, fn, iters)
+    sumL = int(lens.sum())
+    alg = sumL * heads * hd * 2 * 2 + rows * heads * hd * 2 * 2 + int(((lens + 15) // 16).sum()) * 4
+    hbm, _, src = peaks()
+    gbs = alg / (ms * 1e-3) / 1e9
+    return {"kernel": "attn_decode_paged_kernel<bf16,64>", "rows": rows, "sum_kv_len": sumL, "ms": ms,
+            "algorithmic_bytes": alg, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm, "peak_source": src}
+
+
+def bench_gemm(ak, torch, iters, small):
+    res = []
+    M, K = (4096 if small else 32768), 768
+    _, tf, src = peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    for N in (2304, 3072, 50257):
+        a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        wt = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ak.ops.gemm_bf16(a, wt, c, M, N, K, ak.EPI_STORE_BF16, stream)
+        ms = timed(torch, fn, max(3, iters // (8 if N > 10000 else 1)))
+        fl = 2.0 * M * N * K
+        t = fl / (ms * 1e-3) / 1e12
+        res.append({"kernel": "gemm_bf16_kernel (tcgen05)", "m": M, "n": N, "k": K, "ms": ms, "TFLOP/s": t,
+                    "peak_TFLOP/s": tf, "frac": t / tf, "peak_source": src})
+        del a, wt, c
+    return res
+
+
+def bench_norm(ak, torch, iters, small):
+    rows, size, hd = (8192 if small else 32768), 768, 64
+    nbuf = 4  # rotate buffers: 4 x (100 MB in + 50 MB out) > L2
+    xs = [torch.randn(rows, size, device="cuda") for _ in range(nbuf)]
+    rs = [torch.randn(rows, size, device="cuda") for _ in range(nbuf)]
+    ys = [torch.empty(rows, size, device="cuda", dtype=torch.bfloat16) for _ in range(nbuf)]
+    w = torch.ones(size, device="cuda")
+    pos = (torch.arange(rows, device="cuda", dtype=torch.int32) % 512).contiguous()
+    stream = torch.cuda.current_stream().cuda_stream
+    hbm, _, src = peaks()
+    out = []
+    for name, use_res, use_rope in (("rmsnorm", False, False), ("rmsnorm+rope", False, True),
+                                    ("rmsnorm+rope+residual", True, True)):
+        it = [0]
+
+        def fn():
+            i = it[0] % nbuf
+            it[0] += 1
+            ak.ops.rmsnorm_rope_residual(xs[i], rs[i] if use_res else None, w, ys[i], pos if use_rope else None, rows,
+                                         size, 1e-5, hd if use_rope else 0, ak.AK_BF16, stream)
+        ms = timed(torch, fn, iters)
+        alg = rows * size * (4 + 2) + (rows * size * 8 if use_res else 0)
+        gbs = alg / (ms * 1e-3) / 1e9
+        out.append({"kernel": f"rmsnorm_rows_kernel ({name})", "rows": rows, "size": size, "ms": ms,
+                    "algorithmic_bytes": alg, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm, "peak_source": src})
+    return out
+
+
+def bench_engine(ak, torch, iters, small):
+    """Steady-state decode steps of the 162M engine (64 sequences in flight, ragged lengths):
+    the launch sequence a profiler should look at. Admits 64 prompts, runs `warm` steps, then
+    times `iters` decode-only steps (captured graph) with host wall clock around each step."""
+    import time
+    cfg = ak.ModelConfig.akasha_hall_1()
+    ctx = ak.Context(0)
+    w = ak.ModelWeights(ctx, cfg, ak.AK_BF16)
+    w.init_synthetic(0, 0.02)
+    eng = ak.Engine(ctx, w, max_seqs=64, max_seq_len=512, use_cuda_graph=True, attn_timing=True)
+    lens = ak.uniform_ints(64, 16, 448, seed=2)
+    for i, l in enumerate(lens):
+        eng.submit(ak.uniform_tokens(int(l), cfg.vocab_size, seed=100 + i), 512)
+    warm = 4 if small else 40
+    for _ in range(warm):
+        eng.step()
+    eng.reset_stats()
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        eng.step()
+    dt = (time.perf_counter() - t0) / iters
+    st = eng.stats()
+    out = {"kernel": "engine decode step (162M, 64 seqs)", "ms_per_step": dt * 1e3, "tok/s": 64 / dt,
+           "kernels_per_step": st["kernel_launches"] / max(1, st["steps"]),
+           "attn_us_layer0": 1e3 * st["attn_ms_total"] / max(1, st["attn_launches_timed"]),
+           "attn_GB/s": st["attn_bytes_total"] / max(1e-9, st["attn_ms_total"] * 1e-3) / 1e9}
+    eng.close(); w.close(); ctx.close()
+    return out
+
+
+def main():
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    ak = entry.load_package()
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    iters = 20
+    if "--iters" in sys.argv:
+        iters = int(sys.argv[sys.argv.index("--iters") + 1])
+        args = [a for a in args if a != str(iters)]
+    small = "--small" in sys.argv
+    which = args or ["attn", "gemm", "norm"]
+    torch.cuda.set_device(0)
+    for w in which:
+        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine}[w](ak, torch, iters, small)
+        for line in (r if isinstance(r, list) else [r]):
+            print(json.dumps(line))
+    torch.cuda.synchronize()
+    ak.check(ak.lib().ak_check_device_status(None))
+
+
+if __name__ == "__main__":
+    main()

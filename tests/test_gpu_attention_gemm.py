@@ -142,7 +142,7 @@ def test_rope_kv_append(ak, orc, torch_cuda, dtype, heads, hd):
             assert np.max(np.abs(gk[b, :, w, :].reshape(-1) - k)) < tol * 4
             assert np.max(np.abs(gv[b, :, w, :].reshape(-1) - v)) < tol * 4
     # every slot that was not addressed is untouched
-    assert (gk[~written] == 9.0).all() and (gv[~written] == 9.0).all()
+    assert (gk.transpose(0, 2, 1, 3)[~written] == 9.0).all() and (gv.transpose(0, 2, 1, 3)[~written] == 9.0).all()
 
 
 # -------------------------------------------------------------------------------- tcgen05 GEMM
