@@ -1,6 +1,7 @@
 """Kernel microbenchmarks (one JSON line per kernel), timed with CUDA events on the launching stream.
 
     python akasha-core_b200/microbench.py [attn] [gemm] [norm] [engine] [--iters N] [--small]
+                                          [--rows R] [--splits S] [--min-len L]   (attn only)
 
   attn : ragged paged decode attention, 1024 sequences, 12 heads x 64, KV lengths U[1,512] (seed 3),
          bf16 K/V ~ N(0,1), block 16.  Reports algorithmic GB/s against the measured HBM peak.
@@ -34,6 +35,11 @@ def peaks():
     return 6650.0, 1590.0, "fallback"
 
 
+def _opt(name, default):
+    """Value of a `--name value` command-line option."""
+    return sys.argv[sys.argv.index(name) + 1] if name in sys.argv else default
+
+
 def timed(torch, fn, iters, warmup=3):
     st = torch.cuda.current_stream()
     for _ in range(warmup):
@@ -50,7 +56,10 @@ def timed(torch, fn, iters, warmup=3):
 
 def bench_attn(ak, torch, iters, small):
     rows, heads, hd, max_blocks = (256 if small else 1024), 12, 64, 32
-    lens = ak.uniform_ints(rows, 1, 512, seed=3)
+    rows = int(_opt("--rows", rows))
+    splits = int(_opt("--splits", 1))
+    lo = int(_opt("--min-len", 1))
+    lens = ak.uniform_ints(rows, lo, 512, seed=3)
     n_blocks = rows * max_blocks
     g = torch.Generator(device="cuda").manual_seed(3)
     kp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
@@ -60,14 +69,16 @@ def bench_attn(ak, torch, iters, small):
     out = torch.empty_like(q)
     kv_lens = torch.from_numpy(lens.astype(np.int32)).cuda()
     stream = torch.cuda.current_stream().cuda_stream
+    nb = ak.ops.attn_decode_scratch_bytes(rows, heads, hd, max_blocks, splits, ak.AK_BF16)
+    scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device="cuda")
     fn = lambda: ak.ops.attn_decode_paged(q, kp, vp, perm, kv_lens, out, rows, heads, hd, max_blocks, 0.125,
-                                          ak.AK_BF16, 1, n_blocks, None, stream)
+                                          ak.AK_BF16, splits, n_blocks, scratch, stream)
     ms = timed(torch, fn, iters)
     sumL = int(lens.sum())
     alg = sumL * heads * hd * 2 * 2 + rows * heads * hd * 2 * 2 + int(((lens + 15) // 16).sum()) * 4
     hbm, _, src = peaks()
     gbs = alg / (ms * 1e-3) / 1e9
-    return {"kernel": "attn_decode_paged_kernel<bf16,64>", "rows": rows, "sum_kv_len": sumL, "ms": ms,
+    return {"kernel": "attn_decode_paged_kernel<bf16,64>", "rows": rows, "n_splits": splits, "sum_kv_len": sumL, "ms": ms,
             "algorithmic_bytes": alg, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm, "peak_source": src}
 
 
@@ -153,11 +164,8 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     ak = entry.load_package()
-    args = [a for a in sys.argv[1:] if not a.startswith("--")]
-    iters = 20
-    if "--iters" in sys.argv:
-        iters = int(sys.argv[sys.argv.index("--iters") + 1])
-        args = [a for a in args if a != str(iters)]
+    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine")]
+    iters = int(_opt("--iters", 20))
     small = "--small" in sys.argv
     which = args or ["attn", "gemm", "norm"]
     torch.cuda.set_device(0)
