@@ -108,6 +108,7 @@ _PROTOS = {
     "ak_silu": [vp, vp, C.c_uint32],
     "ak_argmax": [vp, vp, C.c_uint32, C.c_uint32, vp],
     "ak_attn_decode_paged": [vp, vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
+    "ak_attn_decode_paged_noalloc": [vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
     "ak_rope_kv_append": [vp, vp, vp, vp, vp, vp, vp] + [C.c_uint32] * 5,
     "ak_rmsnorm_rope_residual": [vp, vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32, C.c_uint32],
     "ak_gemm_bf16": [vp, vp, vp, vp, MatMulMeta, C.c_uint32],
@@ -168,6 +169,8 @@ def lib() -> C.CDLL:
         L.ak_session_cur_len.restype = C.c_uint32
         L.ak_attn_decode_scratch_bytes.argtypes = [C.POINTER(AttnDecodeParams)]
         L.ak_attn_decode_scratch_bytes.restype = C.c_size_t
+        L.ak_attn_decode_noalloc_max_scratch_bytes.argtypes = []
+        L.ak_attn_decode_noalloc_max_scratch_bytes.restype = C.c_size_t
         _lib = L
     return _lib
 

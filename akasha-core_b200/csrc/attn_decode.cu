@@ -450,3 +450,58 @@ int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool, const 
     return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p);
 }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free variant of the split-KV decode attention.
+//
+// Some hosts may not allocate device memory at the moment they need attention: a plugin running
+// inside somebody else's memory pool, a real-time loop that forbids allocator calls after start-up,
+// or code running where the process has already handed all free HBM to a KV pool. For them the
+// split-KV partials live in a fixed buffer that is part of the loaded library image, so the call
+// needs no workspace from the caller and performs no cudaMalloc / cudaFree.
+//
+// The buffer is a file-scope __device__ array: every GPU that loads this library holds
+// AK_NOALLOC_SCRATCH_BYTES of it until the process exits. In host code the array's NAME is only
+// a host-side handle, not a device address, so the address is looked up once per device with
+// cudaGetSymbolAddress (with that device current) and that pointer is what the kernels receive.
+namespace ak {
+constexpr size_t AK_NOALLOC_SCRATCH_BYTES = 8u << 20;  // 8 MiB of partials
+static __device__ __align__(256) unsigned char g_noalloc_scratch[AK_NOALLOC_SCRATCH_BYTES];
+
+static int noalloc_scratch_ptr(void** out) {
+    static void* ptrs[64] = {};
+    int dev = 0;
+    AK_CUDA(cudaGetDevice(&dev));
+    AK_REQUIRE(dev >= 0 && dev < 64, AK_ERR_UNSUPPORTED, "attn_decode_paged_noalloc: device index %d not supported", dev);
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        AK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+        AK_REQUIRE(p != nullptr, AK_ERR_CUDA, "attn_decode_paged_noalloc: symbol address lookup returned null");
+        ptrs[dev] = p;
+    }
+    *out = ptrs[dev];
+    return AK_OK;
+}
+}  // namespace ak
+
+extern "C" {
+size_t ak_attn_decode_noalloc_max_scratch_bytes(void) { return AK_NOALLOC_SCRATCH_BYTES; }
+
+int ak_attn_decode_paged_noalloc(void* stream, const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_tables, const int32_t* kv_lens, void* out, ak_attn_decode_params p) {
+    AK_REQUIRE(q && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_paged_noalloc: null pointer");
+    const uint32_t ns = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.max_blocks_per_seq * DEC_BS);
+    const size_t need = attn_decode_scratch_bytes(p.rows, p.heads, p.head_dim, ns);
+    AK_REQUIRE(need <= AK_NOALLOC_SCRATCH_BYTES, AK_ERR_UNSUPPORTED,
+               "ak_attn_decode_paged_noalloc: rows*heads*n_splits*(head_dim+2)*4 = %zu bytes of split partials exceed the built-in "
+               "%zu-byte buffer; lower n_splits or use ak_attn_decode_paged with caller scratch",
+               need, (size_t)AK_NOALLOC_SCRATCH_BYTES);
+    void* scratch = nullptr;
+    int rc = noalloc_scratch_ptr(&scratch);
+    if (rc) return rc;
+    p.n_splits = ns;
+    // Every partial the merge kernel reads is written by the split kernel of the same call, so the
+    // buffer's previous contents never matter and nothing has to be cleared.
+    return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p);
+}
+}

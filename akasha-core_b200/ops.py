@@ -95,6 +95,21 @@ def attn_decode_paged(q, k_pool, v_pool, block_tables, kv_lens, out, rows, heads
                                      _p(out), _p(scratch), p))
 
 
+def attn_decode_paged_noalloc(q, k_pool, v_pool, block_tables, kv_lens, out, rows, heads, head_dim, max_blocks_per_seq,
+                              scale, kv_dtype=AK_BF16, n_splits=0, pool_blocks=0, stream=None):
+    """`attn_decode_paged` for callers that must not allocate: the split-KV partials live in a
+    fixed buffer inside the library (8 MiB per GPU), no scratch argument, no cudaMalloc. Raises
+    `Unsupported` when the partials would not fit. Calls that can overlap on one GPU share the
+    buffer and must be ordered by the caller; make the first call on a device outside any capture."""
+    p = AttnDecodeParams(rows, heads, head_dim, 16, max_blocks_per_seq, scale, kv_dtype, n_splits, pool_blocks)
+    check(lib().ak_attn_decode_paged_noalloc(_s(stream), _p(q), _p(k_pool), _p(v_pool), _p(block_tables),
+                                             _p(kv_lens), _p(out), p))
+
+
+def attn_decode_noalloc_max_scratch_bytes() -> int:
+    return int(lib().ak_attn_decode_noalloc_max_scratch_bytes())
+
+
 def rope_kv_append(qkv, positions, slots, q_out, k_pool, v_pool, tokens, heads, head_dim, kv_dtype=AK_BF16,
                    stream=None):
     check(lib().ak_rope_kv_append(_s(stream), _p(qkv), _p(positions), _p(slots), _p(q_out), _p(k_pool), _p(v_pool),

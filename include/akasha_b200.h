@@ -171,6 +171,25 @@ AK_API int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool,
                                 const int32_t* block_tables, const int32_t* kv_lens, void* out,
                                 void* scratch, ak_attn_decode_params p);
 
+/* The same attention for callers that cannot allocate device memory when they call it (a plugin
+ * living inside another framework's memory pool, a loop that bans allocator calls after start-up,
+ * a process whose free HBM has all gone to the KV pool). It has no counterpart in the reference.
+ * The split-KV partials go to a buffer built into the library image instead of caller scratch:
+ *   - each GPU that loads the library holds that buffer (ak_attn_decode_noalloc_max_scratch_bytes(),
+ *     8 MiB) until the process exits;
+ *   - a launch whose partials (rows*heads*n_splits*(head_dim+2)*4 bytes) do not fit is refused with
+ *     AK_ERR_UNSUPPORTED and a message; nothing is launched;
+ *   - the call makes no cudaMalloc/cudaFree and calls no allocating library routine;
+ *   - the first call on a device looks up the buffer's device address (that device must be
+ *     current); make that first call before starting any stream capture;
+ *   - all calls on one GPU share the buffer: calls that may overlap on the GPU (different streams)
+ *     race on it and must be ordered by the caller. Nothing needs clearing between calls: every
+ *     partial that is read was written earlier in the same call. */
+AK_API size_t ak_attn_decode_noalloc_max_scratch_bytes(void);
+AK_API int ak_attn_decode_paged_noalloc(void* stream, const void* q, const void* k_pool, const void* v_pool,
+                                        const int32_t* block_tables, const int32_t* kv_lens, void* out,
+                                        ak_attn_decode_params p);
+
 /* Fused head split + RoPE + paged KV append (head_gather x3, rope(_offset) x2, cache_write x2:
  * src/nn/inference_graphs.rs:241-269, 385-426) over a ragged token batch.
  *   qkv [tokens, 3*dim] f32;  positions int32[tokens];  slots int32[tokens] (paged slot of the
