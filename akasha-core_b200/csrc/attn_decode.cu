@@ -62,6 +62,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                          const T* __restrict__ q, const int32_t* __restrict__ block_tables,
                          const int32_t* __restrict__ kv_lens, T* __restrict__ out, float* __restrict__ scratch,
                          uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits) {
+    pdl_wait();
+    pdl_trigger();
     using C = DecCfg<T, HD>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[DEC_WARPS][C::STAGES];
@@ -259,6 +261,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 template <typename T, int HD>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, uint32_t heads,
                                            uint32_t n_splits) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int EPL = HD / 32;
     const uint32_t h = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
     const float* base = scratch + ((size_t)row * heads + h) * n_splits * (HD + 2);
@@ -289,6 +293,8 @@ __global__ void attn_decode_generic_kernel(const T* __restrict__ q, const T* __r
                                            const T* __restrict__ v_pool, const int32_t* __restrict__ block_tables,
                                            const int32_t* __restrict__ kv_lens, T* __restrict__ out, uint32_t heads,
                                            uint32_t hd, uint32_t bs, uint32_t max_blocks, float scale) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ float sc[];  // kv_len scores
     __shared__ float red[32];
     const uint32_t h = blockIdx.x, row = blockIdx.y;
@@ -373,15 +379,11 @@ static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const
         attr_set[dev & 63] = true;
     }
     dim3 grid(p.heads, p.rows, n_splits);
-    attn_decode_paged_kernel<T, HD><<<grid, DEC_WARPS * 32, C::SMEM_BYTES, st>>>(
-        tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+    AK_TRY(launch_k(attn_decode_paged_kernel<T, HD>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, 
+        tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits));
     if (n_splits > 1) {
         dim3 g2(p.heads, p.rows);
-        attn_decode_combine_kernel<T, HD><<<g2, 32, 0, st>>>((const float*)scratch, (T*)out, p.heads, n_splits);
-        AK_COUNT_LAUNCH();
-        AK_CHECK_LAUNCH();
+        AK_TRY(launch_k(attn_decode_combine_kernel<T, HD>, dim3(g2), dim3(32), 0, st, NO_CLUSTER, (const float*)scratch, (T*)out, p.heads, n_splits));
     }
     return AK_OK;
 }
@@ -408,15 +410,13 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
         dim3 grid(p.heads, p.rows);
         if (p.kv_dtype == AK_F32) {
             if (smem > 48 * 1024) AK_CUDA(cudaFuncSetAttribute(attn_decode_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attn_decode_generic_kernel<float><<<grid, 128, smem, st>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, kv_lens,
-                                                                       (float*)out, p.heads, p.head_dim, p.block_size, p.max_blocks_per_seq, p.scale);
+            AK_TRY(launch_k(attn_decode_generic_kernel<float>, dim3(grid), dim3(128), smem, st, NO_CLUSTER, (const float*)q, (const float*)k_pool, (const float*)v_pool, block_tables, kv_lens,
+                                                                       (float*)out, p.heads, p.head_dim, p.block_size, p.max_blocks_per_seq, p.scale));
         } else {
             if (smem > 48 * 1024) AK_CUDA(cudaFuncSetAttribute(attn_decode_generic_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            attn_decode_generic_kernel<bf16><<<grid, 128, smem, st>>>((const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, kv_lens,
-                                                                      (bf16*)out, p.heads, p.head_dim, p.block_size, p.max_blocks_per_seq, p.scale);
+            AK_TRY(launch_k(attn_decode_generic_kernel<bf16>, dim3(grid), dim3(128), smem, st, NO_CLUSTER, (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, block_tables, kv_lens,
+                                                                      (bf16*)out, p.heads, p.head_dim, p.block_size, p.max_blocks_per_seq, p.scale));
         }
-        AK_COUNT_LAUNCH();
-        AK_CHECK_LAUNCH();
         return AK_OK;
     }
     uint32_t n_splits = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.max_blocks_per_seq * DEC_BS);

@@ -36,6 +36,8 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
                     const int32_t* __restrict__ block_tables, uint32_t max_blocks, const int32_t* __restrict__ cu,
                     const int32_t* __restrict__ seq_slot, T* __restrict__ out, float* __restrict__ l_cache,
                     uint32_t row_base, uint32_t heads, float scale, uint32_t fixed_len) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int EPC = 16 / (int)sizeof(T);
     constexpr int CPR = HD / EPC;      // 16-byte chunks per row
     constexpr int OC = HD / 16;        // output columns per thread
@@ -199,6 +201,8 @@ __global__ void attn_prefill_generic_kernel(const T* __restrict__ q, const T* __
                                             const int32_t* __restrict__ seq_slot, T* __restrict__ out,
                                             float* __restrict__ l_cache, uint32_t row_base, uint32_t heads, uint32_t hd,
                                             float scale, uint32_t fixed_len) {
+    pdl_wait();
+    pdl_trigger();
     extern __shared__ float sc[];  // (qi+1) scores
     const uint32_t seq = blockIdx.z, h = blockIdx.y, qi = blockIdx.x, lane = threadIdx.x;
     const uint32_t dim = heads * hd;
@@ -252,10 +256,8 @@ static int launch_tiled(cudaStream_t st, const T* q, const T* k, const T* v, con
         attr_set[dev & 63] = true;
     }
     dim3 grid(cdiv(max_len, PF_BQ), heads, n_seqs);
-    attn_prefill_kernel<T, HD, PAGED><<<grid, PF_THREADS, smem, st>>>(q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache,
-                                                                       row_base, heads, scale, fixed_len);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+    AK_TRY(launch_k(attn_prefill_kernel<T, HD, PAGED>, dim3(grid), dim3(PF_THREADS), smem, st, NO_CLUSTER, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache,
+                                                                       row_base, heads, scale, fixed_len));
     return AK_OK;
 }
 
@@ -268,10 +270,8 @@ static int launch_generic(cudaStream_t st, const T* q, const T* k, const T* v, c
     if (smem > 48 * 1024)
         AK_CUDA(cudaFuncSetAttribute(attn_prefill_generic_kernel<T, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid(max_len, heads, n_seqs);
-    attn_prefill_generic_kernel<T, PAGED><<<grid, 32, smem, st>>>(q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache, row_base,
-                                                                  heads, hd, scale, fixed_len);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+    AK_TRY(launch_k(attn_prefill_generic_kernel<T, PAGED>, dim3(grid), dim3(32), smem, st, NO_CLUSTER, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache, row_base,
+                                                                  heads, hd, scale, fixed_len));
     return AK_OK;
 }
 

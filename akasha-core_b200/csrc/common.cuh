@@ -22,6 +22,12 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 
 #define AK_CHECK_LAUNCH() AK_CUDA(cudaGetLastError())
 
+#define AK_TRY(expr)              \
+    do {                          \
+        int _rc = (expr);         \
+        if (_rc) return _rc;      \
+    } while (0)
+
 #define AK_REQUIRE(cond, code, ...)    \
     do {                               \
         if (!(cond)) {                 \
@@ -33,6 +39,13 @@ int cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 static inline unsigned cdiv(unsigned a, unsigned b) { return (a + b - 1) / b; }
 static inline size_t cdiv64(size_t a, size_t b) { return (a + b - 1) / b; }
+
+// Programmatic dependent launch (PDL): kernels of the per-step chain are launched with the
+// programmatic-stream-serialization attribute, call pdl_wait() before touching global memory
+// (it returns once every prerequisite grid has completed and flushed) and pdl_trigger() right
+// after, which lets the NEXT kernel's blocks be scheduled early and run their prologue while this
+// grid drains. Without the launch attribute both instructions are no-ops.
+bool pdl_enabled();
 
 // Number of kernel launches issued by this library on the calling thread (for the benchmark's
 // `gpu_launches` claim).
@@ -54,6 +67,9 @@ template <> struct Cvt<bf16> {
     __device__ static __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
     __device__ static __forceinline__ bf16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
+
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -128,6 +144,38 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, u
                  "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
 }
+
+// Launch helper for the per-step chain: optional thread-block cluster, PDL attribute when enabled.
+template <typename... KArgs, typename... Args>
+static inline int launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, dim3 cluster,
+                           Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    unsigned na = 0;
+    if (cluster.x * cluster.y * cluster.z > 0) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = cluster.x;
+        attr[na].val.clusterDim.y = cluster.y;
+        attr[na].val.clusterDim.z = cluster.z;
+        na++;
+    }
+    if (pdl_enabled()) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<Args&&>(args)...);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaLaunchKernelEx", __FILE__, __LINE__);
+    AK_COUNT_LAUNCH();
+    return AK_OK;
+}
+static const dim3 NO_CLUSTER(0, 0, 0);
 
 #endif  // __CUDACC__
 

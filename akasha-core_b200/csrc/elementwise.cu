@@ -30,6 +30,8 @@ template <typename WT>
 __global__ void embed_rows_kernel(const int32_t* __restrict__ tok_src, uint32_t idx_stride,
                                   const uint32_t* __restrict__ sampled, const WT* __restrict__ table,
                                   float* __restrict__ hidden, uint32_t vocab, uint32_t dim) {
+    pdl_wait();
+    pdl_trigger();
     uint32_t r = blockIdx.x;
     int32_t ts = tok_src[(size_t)r * idx_stride];
     // INT32_MIN marks an inactive row: it must not be decoded as a slot reference
@@ -47,11 +49,9 @@ int launch_embed_rows(cudaStream_t st, const int32_t* tok_src, uint32_t idx_stri
                       uint32_t rows) {
     if (rows == 0) return AK_OK;
     if (table_dtype == AK_F32)
-        embed_rows_kernel<float><<<rows, 256, 0, st>>>(tok_src, idx_stride, sampled, (const float*)table, hidden, vocab, dim);
+        AK_TRY(launch_k(embed_rows_kernel<float>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const float*)table, hidden, vocab, dim));
     else
-        embed_rows_kernel<bf16><<<rows, 256, 0, st>>>(tok_src, idx_stride, sampled, (const bf16*)table, hidden, vocab, dim);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+        AK_TRY(launch_k(embed_rows_kernel<bf16>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const bf16*)table, hidden, vocab, dim));
     return AK_OK;
 }
 
@@ -63,6 +63,8 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
                                     const float* __restrict__ w, OT* __restrict__ y,
                                     const int32_t* __restrict__ row_map, const int32_t* __restrict__ positions,
                                     uint32_t rows, uint32_t size, float eps, uint32_t head_dim) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int RCACHE = 8;  // float4 per lane kept in registers -> size <= 1024 cached
     uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     uint32_t lane = threadIdx.x & 31;
@@ -160,15 +162,13 @@ static int rmsnorm_dispatch(cudaStream_t st, float* x, const float* residual, co
     dim3 grid(cdiv(rows, WARPS)), block(WARPS * 32);
     bool rope = head_dim != 0;
     if (residual && rope)
-        rmsnorm_rows_kernel<OT, true, true><<<grid, block, 0, st>>>(x, residual, w, y, row_map, positions, rows, size, eps, head_dim);
+        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, true, true>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
     else if (residual)
-        rmsnorm_rows_kernel<OT, true, false><<<grid, block, 0, st>>>(x, residual, w, y, row_map, positions, rows, size, eps, head_dim);
+        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, true, false>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
     else if (rope)
-        rmsnorm_rows_kernel<OT, false, true><<<grid, block, 0, st>>>(x, residual, w, y, row_map, positions, rows, size, eps, head_dim);
+        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, false, true>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
     else
-        rmsnorm_rows_kernel<OT, false, false><<<grid, block, 0, st>>>(x, residual, w, y, row_map, positions, rows, size, eps, head_dim);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, false, false>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
     return AK_OK;
 }
 
@@ -311,6 +311,8 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int32
                                       T* __restrict__ k_pool, T* __restrict__ v_pool,
                                       const float2* __restrict__ rope_table, uint32_t rope_table_len,
                                       uint32_t tokens, uint32_t heads, uint32_t hd, uint32_t bs, uint32_t idx_stride) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int VEC = 16 / sizeof(T);
     uint32_t chunks_per_head = hd / VEC;
     uint32_t dim = heads * hd;
@@ -376,17 +378,15 @@ int launch_rope_kv_append(cudaStream_t st, const float* qkv, const int32_t* posi
     AK_REQUIRE(head_dim % 8 == 0, AK_ERR_UNSUPPORTED, "rope_kv_append: head_dim must be a multiple of 8");
     if (kv_dtype == AK_F32) {
         size_t total = (size_t)tokens * heads * (head_dim / 4);
-        rope_kv_append_kernel<float><<<(unsigned)cdiv64(total, 256), 256, 0, st>>>(
+        AK_TRY(launch_k(rope_kv_append_kernel<float>, dim3((unsigned)cdiv64(total, 256)), dim3(256), 0, st, NO_CLUSTER, 
             qkv, positions, slots, (float*)q_out, (float*)k_pool, (float*)v_pool, rope_table, rope_table_len, tokens,
-            heads, head_dim, block_size, idx_stride);
+            heads, head_dim, block_size, idx_stride));
     } else {
         size_t total = (size_t)tokens * heads * (head_dim / 8);
-        rope_kv_append_kernel<bf16><<<(unsigned)cdiv64(total, 256), 256, 0, st>>>(
+        AK_TRY(launch_k(rope_kv_append_kernel<bf16>, dim3((unsigned)cdiv64(total, 256)), dim3(256), 0, st, NO_CLUSTER, 
             qkv, positions, slots, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, rope_table, rope_table_len, tokens,
-            heads, head_dim, block_size, idx_stride);
+            heads, head_dim, block_size, idx_stride));
     }
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
     return AK_OK;
 }
 
@@ -398,6 +398,8 @@ __device__ __forceinline__ void argmax_combine(float& v, uint32_t& i, float ov, 
 }
 __global__ void argmax_kernel(const float* __restrict__ logits, uint32_t n, uint32_t ld,
                               const int32_t* __restrict__ row_active, uint32_t* __restrict__ out_idx) {
+    pdl_wait();
+    pdl_trigger();
     uint32_t row = blockIdx.x;
     if (row_active && row_active[row] < 0) return;
     const float* l = logits + (size_t)row * ld;
@@ -434,9 +436,38 @@ __global__ void argmax_kernel(const float* __restrict__ logits, uint32_t n, uint
 int launch_argmax(cudaStream_t st, const float* logits, uint32_t rows, uint32_t n, uint32_t ld,
                   const int32_t* row_active, uint32_t* out_idx) {
     if (rows == 0 || n == 0) return AK_OK;
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, n, ld, row_active, out_idx);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+    AK_TRY(launch_k(argmax_kernel, dim3(rows), dim3(1024), 0, st, NO_CLUSTER, logits, n, ld, row_active, out_idx));
+    return AK_OK;
+}
+
+// Second stage of the argmax fused into the lm_head GEMM: one warp per row reduces the per-tile
+// (max, first index) partials; equal maxima resolve to the lowest index.
+__global__ void argmax_finish_kernel(const float* __restrict__ pv, const uint32_t* __restrict__ pi, uint32_t rows,
+                                     uint32_t tiles, const int32_t* __restrict__ row_active, uint32_t* __restrict__ out_idx) {
+    pdl_wait();
+    pdl_trigger();
+    uint32_t row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    if (row_active && row_active[row] < 0) return;
+    float best = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t t = lane; t < tiles; t += 32) {
+        float v = pv[(size_t)row * tiles + t];
+        uint32_t i = pi[(size_t)row * tiles + t];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        argmax_combine(best, bi, ov, oi);
+    }
+    if (lane == 0) out_idx[row] = (bi == 0xffffffffu) ? 0u : bi;
+}
+int launch_argmax_finish(cudaStream_t st, const float* part_val, const uint32_t* part_idx, uint32_t rows, uint32_t tiles,
+                         const int32_t* row_active, uint32_t* out_idx) {
+    if (rows == 0) return AK_OK;
+    AK_TRY(launch_k(argmax_finish_kernel, dim3(cdiv(rows, 4)), dim3(128), 0, st, NO_CLUSTER, part_val, part_idx, rows, tiles, row_active, out_idx));
     return AK_OK;
 }
 

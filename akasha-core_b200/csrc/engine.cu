@@ -79,6 +79,7 @@ int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak
         return rc;
     }
     e->runner.enable_attn_timing(cfg->attn_timing != 0);
+    e->runner.set_keep_logits(false);
     for (uint32_t b = 0; b < e->cfg.kv_blocks; b++) e->free_blocks.insert((int32_t)b);
     e->slots.assign(cfg->max_seqs, nullptr);
     *out = e;

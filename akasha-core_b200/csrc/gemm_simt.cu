@@ -20,6 +20,8 @@ template <int VEC>
 __global__ void __launch_bounds__(GEMV_WARPS * 32)
 gemv_f32_kernel(const float* __restrict__ x, const float* __restrict__ w, float* __restrict__ y, uint32_t n,
                 uint32_t k, uint32_t flags) {
+    pdl_wait();
+    pdl_trigger();
     constexpr int CT = 32 * VEC;  // columns per CTA
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t ks = cluster.num_blocks();
@@ -113,20 +115,7 @@ static int gemv_launch(cudaStream_t st, const float* x, const float* w, float* y
     if (col_tiles < 296) ks = pow2_floor(296 / col_tiles);
     if (ks > GEMV_MAX_KS) ks = GEMV_MAX_KS;
     while (ks > 1 && k / ks < 2 * GEMV_WARPS) ks /= 2;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(col_tiles, ks, 1);
-    cfg.blockDim = dim3(GEMV_WARPS * 32, 1, 1);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = ks;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    AK_CUDA(cudaLaunchKernelEx(&cfg, gemv_f32_kernel<VEC>, x, w, y, n, k, flags));
-    AK_COUNT_LAUNCH();
-    return AK_OK;
+    return launch_k(gemv_f32_kernel<VEC>, dim3(col_tiles, ks, 1), dim3(GEMV_WARPS * 32), 0, st, dim3(1, ks, 1), x, w, y, n, k, flags);
 }
 
 static int launch_gemv_f32(cudaStream_t st, const float* x, const float* w, float* y, uint32_t n, uint32_t k, uint32_t flags) {
@@ -144,6 +133,8 @@ constexpr int BM = 64, BN = 64, BK = 16;
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c, uint32_t m, uint32_t n,
                 uint32_t k, uint32_t flags) {
+    pdl_wait();
+    pdl_trigger();
     __shared__ float As[BK][BM + 4];  // transposed A tile
     __shared__ float Bs[BK][BN + 4];
     const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -207,9 +198,7 @@ int launch_gemm_f32(cudaStream_t st, const float* a, const float* b, float* c, u
     if (m == 0 || n == 0) return AK_OK;
     if (m == 1 && k > 0) return launch_gemv_f32(st, a, b, c, n, k, flags);
     dim3 grid(cdiv(n, BN), cdiv(m, BM));
-    gemm_f32_kernel<<<grid, 256, 0, st>>>(a, b, c, m, n, k, flags);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
+    AK_TRY(launch_k(gemm_f32_kernel, dim3(grid), dim3(256), 0, st, NO_CLUSTER, a, b, c, m, n, k, flags));
     return AK_OK;
 }
 

@@ -16,6 +16,9 @@
 #include "kernels.h"
 #include "tma.h"
 
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
+
 namespace ak {
 
 __device__ unsigned int g_gemm_status = 0;
@@ -77,32 +80,118 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+constexpr int G_MAX_STAGES = 8;
+
+// Cluster-wide barrier for all threads of all CTAs of the cluster. The .aligned forms need every
+// thread of a warp to execute them together, and the producer / MMA lanes run ahead of their
+// warps, so each warp is re-converged first.
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 template <int BN> struct GemmCfg {
     static constexpr int A_BYTES = GB_M * GB_K * 2;   // 16 KB
     static constexpr int B_BYTES = BN * GB_K * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
-    static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // multiple of 1024 for every BN % 8 == 0
+    static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
+    static constexpr int RED_BYTES = GB_M * BN * 4;   // split-K exchange buffer [src][128][BN/ks]
 };
 
+// Epilogue arguments (by value).
+struct GemmEpi {
+    void* c;            // output matrix (f32 or bf16), may be null for the argmax-only epilogue
+    uint32_t ldc;
+    float* amax_val;    // [m][amax_ld] per-tile row maxima (argmax epilogues)
+    uint32_t* amax_idx; // [m][amax_ld] their column indices
+    uint32_t amax_ld;
+};
+
+enum { EPI_ARGMAX = 4, EPI_STORE_F32_ARGMAX = 5 };
+
+// Store W consecutive accumulator columns of one row with the epilogue op. gcol % 4 == 0.
+template <int EPI, int W>
+__device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint32_t gcol, const float* v, uint32_t n) {
+    if (EPI == AK_EPI_STORE_F32 || EPI == AK_EPI_ADD_F32 || EPI == EPI_STORE_F32_ARGMAX) {
+        float* dst = reinterpret_cast<float*>(ep.c) + (size_t)row * ep.ldc + gcol;
+        const bool vec = (gcol + W <= n) && ((ep.ldc & 3u) == 0);
+        if (vec) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                float4 o = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (EPI == AK_EPI_ADD_F32) {
+                    float4 p = *reinterpret_cast<float4*>(dst + j);
+                    o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++)
+                if (gcol + j < n) {
+                    float o = v[j];
+                    if (EPI == AK_EPI_ADD_F32) o += dst[j];
+                    dst[j] = o;
+                }
+        }
+    } else if (EPI == AK_EPI_STORE_BF16 || EPI == AK_EPI_SILU_BF16) {
+        bf16* dst = reinterpret_cast<bf16*>(ep.c) + (size_t)row * ep.ldc + gcol;
+        float t[W];
+#pragma unroll
+        for (int j = 0; j < W; j++) t[j] = (EPI == AK_EPI_SILU_BF16) ? v[j] / (1.0f + __expf(-v[j])) : v[j];
+        const bool vec = (gcol + W <= n) && ((ep.ldc & 3u) == 0);
+        if (vec) {
+#pragma unroll
+            for (int j = 0; j < W; j += 4) {
+                bf162 a = __floats2bfloat162_rn(t[j], t[j + 1]), b = __floats2bfloat162_rn(t[j + 2], t[j + 3]);
+                uint2 pk;
+                pk.x = *reinterpret_cast<uint32_t*>(&a);
+                pk.y = *reinterpret_cast<uint32_t*>(&b);
+                *reinterpret_cast<uint2*>(dst + j) = pk;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < W; j++)
+                if (gcol + j < n) dst[j] = __float2bfloat16_rn(t[j]);
+        }
+    }
+}
+
+// Kernel. grid = (n tiles, m tiles, ks); thread-block cluster = (1, 1, ks): the ks CTAs of a
+// cluster split the K range of ONE output tile, exchange their partial accumulators through
+// distributed shared memory (every CTA receives the column slice it owns from every peer) and
+// each reduces and stores its own slice in a fixed source order, so the result does not depend on
+// timing. ks == 1 is the plain one-CTA-per-tile GEMM.
 template <int BN, int EPI>
-__global__ void __launch_bounds__(G_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ cptr,
-                 uint32_t m, uint32_t n, uint32_t k, uint32_t ldc) {
+__global__ void __launch_bounds__(G_THREADS)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmEpi ep,
+                 uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols) {
+    // kseg > 1 (only with a cluster of one CTA): the K range is accumulated in kseg separate TMEM
+    // accumulators that the epilogue adds in order. It reproduces, bit for bit, what a cluster of
+    // kseg CTAs computes for the same (n, k), so a row's result does not depend on how many rows
+    // share the launch.
     using C = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[C::STAGES], empty_bar[C::STAGES], acc_bar;
+    __shared__ uint64_t full_bar[G_MAX_STAGES], empty_bar[G_MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_base_sm;
     __shared__ uint32_t fail_flag;
 
+    cg::cluster_group cluster = cg::this_cluster();
+    const uint32_t ks = cluster.num_blocks();
+    const uint32_t rank = cluster.block_rank();
+
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    float* red = reinterpret_cast<float*>(smem + (size_t)stages * C::STAGE_BYTES);  // used when ks > 1
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m0 = blockIdx.y * GB_M, n0 = blockIdx.x * BN;
-    const uint32_t num_kb = (k + GB_K - 1) / GB_K;
+    const uint32_t num_kb_total = (k + GB_K - 1) / GB_K;
+    const uint32_t per = (num_kb_total + ks - 1) / ks;
+    const uint32_t kb_begin = rank * per < num_kb_total ? rank * per : num_kb_total;
+    const uint32_t num_kb = (kb_begin + per <= num_kb_total) ? per : num_kb_total - kb_begin;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (uint32_t s = 0; s < stages; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
         fail_flag = 0;
         mbar_fence_init();
@@ -110,35 +199,42 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tma_prefetch_desc(&tmB);
     }
     if (warp == 1) {
-        tmem_alloc(&tmem_base_sm, C::TMEM_COLS);
+        tmem_alloc(&tmem_base_sm, tmem_cols);
         tmem_relinquish();
     }
     tc_fence_before();
-    __syncthreads();
+    if (ks > 1) cluster_sync_all();  // peers are running before anyone writes into their shared memory
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sm;
+    // everything above touched only this CTA's shared memory and TMEM; from here on global memory
+    // written by the preceding kernels is read
+    pdl_wait();
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer
         if (lane == 0) {
-            for (uint32_t kb = 0; kb < num_kb; kb++) {
-                const uint32_t s = kb % C::STAGES, ph = (kb / C::STAGES) & 1u;
+            for (uint32_t i = 0; i < num_kb; i++) {
+                const uint32_t s = i % stages, ph = (i / stages) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); break; }
                 uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
                 uint8_t* b_dst = a_dst + C::A_BYTES;
                 mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
-                tma_load_2d(a_dst, &tmA, (int32_t)(kb * GB_K), (int32_t)m0, &full_bar[s]);
-                tma_load_2d(b_dst, &tmB, (int32_t)(kb * GB_K), (int32_t)n0, &full_bar[s]);
+                const int32_t kx = (int32_t)((kb_begin + i) * GB_K);
+                tma_load_2d(a_dst, &tmA, kx, (int32_t)m0, &full_bar[s]);
+                tma_load_2d(b_dst, &tmB, kx, (int32_t)n0, &full_bar[s]);
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (one thread)
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(GB_M, BN);
-            bool ok = true;
-            for (uint32_t kb = 0; kb < num_kb && ok; kb++) {
-                const uint32_t s = kb % C::STAGES, ph = (kb / C::STAGES) & 1u;
-                if (!mbar_wait(&full_bar[s], ph)) { atomicExch(&fail_flag, 2u); ok = false; break; }
+            const uint32_t per_seg = (num_kb + kseg - 1) / kseg;
+            for (uint32_t i = 0; i < num_kb; i++) {
+                const uint32_t seg = i / per_seg, first_of_seg = (i - seg * per_seg) == 0;
+                const uint32_t s = i % stages, ph = (i / stages) & 1u;
+                if (!mbar_wait(&full_bar[s], ph)) { atomicExch(&fail_flag, 2u); break; }
                 tc_fence_after();
                 const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
                 const uint32_t b_addr = a_addr + C::A_BYTES;
@@ -146,74 +242,100 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (uint32_t kk = 0; kk < GB_K / 16; kk++) {
                     // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the address field
-                    tc_mma_f16(tmem_base, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (kb | kk) != 0 ? 1u : 0u);
+                    tc_mma_f16(tmem_base + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                               (first_of_seg && kk == 0) ? 0u : 1u);
                 }
                 tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
             }
-            tc_commit(&acc_bar);           // accumulator complete
+            if (num_kb > 0) tc_commit(&acc_bar);  // accumulator complete
+            else mbar_arrive(&acc_bar);           // nothing to accumulate: this CTA contributes zeros
         }
-    } else {
-        // ---------------- epilogue warps 2..5
-        const uint32_t quad = warp & 3u;  // TMEM lanes [32*quad, 32*quad+32)
-        const bool got = mbar_wait(&acc_bar, 0);
+    }
+
+    // ---------------- epilogue warps 2..5: thread <-> accumulator row (TMEM lane)
+    const uint32_t quad = warp & 3u;
+    const uint32_t trow = quad * 32 + lane;  // row inside the tile
+    const uint32_t row = m0 + trow;
+    bool got = true;
+    if (warp >= 2) {
+        got = mbar_wait(&acc_bar, 0);
         if (!got && lane == 0) atomicExch(&fail_flag, 3u);
         tc_fence_after();
-        const uint32_t row = m0 + quad * 32 + lane;
-        if (got && num_kb > 0) {
+    }
+
+    if (ks == 1) {
+        if (warp >= 2 && got) {
+            float best = -INFINITY;
+            uint32_t best_i = 0xffffffffu;
 #pragma unroll 1
             for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 16) {
                 uint32_t r[16];
-                tmem_ld16(tmem_base + ((quad * 32u) << 16) + c0, r);
-                tmem_ld_wait();
+                float v[16];
+                if (num_kb > 0) {
+                    tmem_ld16(tmem_base + ((quad * 32u) << 16) + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+                    for (uint32_t seg = 1; seg < kseg; seg++) {  // segment order = cluster rank order
+                        tmem_ld16(tmem_base + ((quad * 32u) << 16) + seg * BN + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) v[j] += __uint_as_float(r[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0.0f;
+                }
                 if (row < m) {
-                    const uint32_t col0 = n0 + c0;
-                    if (EPI == AK_EPI_STORE_F32 || EPI == AK_EPI_ADD_F32) {
-                        float* dst = reinterpret_cast<float*>(cptr) + (size_t)row * ldc + col0;
-                        const bool vec = (col0 + 16 <= n) && ((ldc & 3u) == 0);
-                        if (vec) {
+                    if (EPI != EPI_ARGMAX) epi_store<EPI, 16>(ep, row, n0 + c0, v, n);
+                    if (EPI == EPI_ARGMAX || EPI == EPI_STORE_F32_ARGMAX) {
 #pragma unroll
-                            for (int j = 0; j < 16; j += 4) {
-                                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                                if (EPI == AK_EPI_ADD_F32) {
-                                    float4 o = *reinterpret_cast<float4*>(dst + j);
-                                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
-                                }
-                                *reinterpret_cast<float4*>(dst + j) = v;
-                            }
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (col0 + j < n) {
-                                    float v = __uint_as_float(r[j]);
-                                    if (EPI == AK_EPI_ADD_F32) v += dst[j];
-                                    dst[j] = v;
-                                }
-                        }
-                    } else {
-                        bf16* dst = reinterpret_cast<bf16*>(cptr) + (size_t)row * ldc + col0;
-                        float v[16];
-#pragma unroll
-                        for (int j = 0; j < 16; j++) {
-                            v[j] = __uint_as_float(r[j]);
-                            if (EPI == AK_EPI_SILU_BF16) v[j] = v[j] / (1.0f + __expf(-v[j]));
-                        }
-                        const bool vec = (col0 + 16 <= n) && ((ldc & 7u) == 0);
-                        if (vec) {
-                            uint32_t pk[8];
-#pragma unroll
-                            for (int j = 0; j < 8; j++) {
-                                bf162 t = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                pk[j] = *reinterpret_cast<uint32_t*>(&t);
-                            }
-                            *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                            *reinterpret_cast<uint4*>(dst + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < 16; j++)
-                                if (col0 + j < n) dst[j] = __float2bfloat16_rn(v[j]);
-                        }
+                        for (int j = 0; j < 16; j++)
+                            if (n0 + c0 + j < n && v[j] > best) { best = v[j]; best_i = n0 + c0 + j; }
                     }
                 }
+            }
+            if ((EPI == EPI_ARGMAX || EPI == EPI_STORE_F32_ARGMAX) && row < m) {
+                ep.amax_val[(size_t)row * ep.amax_ld + blockIdx.x] = best;
+                ep.amax_idx[(size_t)row * ep.amax_ld + blockIdx.x] = best_i;
+            }
+        }
+    } else {
+        // ---- scatter: columns [d*SL, (d+1)*SL) of my partial go to CTA d's exchange buffer slot `rank`
+        const uint32_t SL = (uint32_t)BN / ks;  // multiple of 4 by construction of the launch
+        if (warp >= 2 && got) {  // warp-uniform: tcgen05.ld is a warp-wide (.aligned) instruction
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 16) {
+                uint32_t r[16];
+                if (num_kb > 0) {
+                    tmem_ld16(tmem_base + ((quad * 32u) << 16) + c0, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) r[j] = 0u;
+                }
+                if (row < m) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; j += 4) {
+                        const uint32_t col = c0 + j, dest = col / SL, off = col - dest * SL;
+                        float* peer = cluster.map_shared_rank(red, dest);
+                        *reinterpret_cast<uint4*>(peer + ((size_t)rank * GB_M + trow) * SL + off) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    }
+                }
+            }
+        }
+        tc_fence_before();
+        cluster_sync_all();  // every partial slice has landed in its owner's shared memory
+        if (warp >= 2 && got && row < m) {
+#pragma unroll 1
+            for (uint32_t j = 0; j < SL; j += 4) {
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (uint32_t src = 0; src < ks; src++) {  // fixed order: deterministic sum
+                    float4 p = *reinterpret_cast<const float4*>(red + ((size_t)src * GB_M + trow) * SL + j);
+                    acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+                }
+                float v[4] = {acc.x, acc.y, acc.z, acc.w};
+                epi_store<EPI, 4>(ep, row, n0 + rank * SL + j, v, n);
             }
         }
     }
@@ -221,71 +343,184 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0 && fail_flag) atomicExch(&g_gemm_status, fail_flag);
-    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Launch configuration.
+struct GemmPlan {
+    uint32_t bn, ks, stages;
+    uint32_t kseg;  // in-CTA K segments (large m with invariant = true), else 1
+};
+
+static constexpr uint32_t SMEM_TWO_PER_SM = 112 * 1024;   // two CTAs fit one SM below this
+static constexpr uint32_t SMEM_ONE_PER_SM = 220 * 1024;
+
+static uint32_t stage_bytes(uint32_t bn) { return GB_M * GB_K * 2 + bn * GB_K * 2; }
+
+// Skinny problems (m <= 128: decode batches) are latency- and weight-stream-bound: pick the
+// tile width / K split that gives one wave of up to 296 CTAs (two per SM) with the shortest K
+// chain per CTA. Large m uses wide tiles and deep pipelines.
+static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, bool invariant = false) {
+    const uint32_t num_kb = cdiv(k, GB_K);
+    GemmPlan p{};
+    p.kseg = 1;
+    if (m > GB_M && invariant && allow_split) {
+        // same K partition as the skinny plan of this (n, k), done inside one CTA
+        const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
+        if (sk.ks > 1) {
+            p.kseg = sk.ks;
+            p.ks = 1;
+            p.bn = 512 / sk.ks > 256 ? 256 : 512 / sk.ks;
+            uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
+            if (st > G_MAX_STAGES) st = G_MAX_STAGES;
+            if (p.bn <= 64 && st > 6) st = 6;
+            p.stages = st < num_kb ? st : num_kb;
+            return p;
+        }
+    }
+    if (m > GB_M) {
+        const uint32_t mt = cdiv(m, GB_M);
+        const uint32_t cands[5] = {256, 128, 64, 32, 16};
+        p.bn = 16;
+        for (int i = 0; i < 5; i++)
+            if ((uint64_t)mt * cdiv(n, cands[i]) >= 148) { p.bn = cands[i]; break; }
+        p.ks = 1;
+        uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
+        if (st > G_MAX_STAGES) st = G_MAX_STAGES;
+        if (p.bn <= 64 && st > 6) st = 6;
+        p.stages = st < num_kb ? st : (num_kb ? num_kb : 1);
+        return p;
+    }
+    const uint32_t slots = 296;
+    if (cdiv(n, 64) > slots) {
+        // very wide n (the lm_head): one wave of wide tiles, two CTAs per SM
+        const uint32_t cands[3] = {128, 176, 256};
+        p.bn = 256;
+        for (int i = 0; i < 3; i++)
+            if (cdiv(n, cands[i]) <= slots) { p.bn = cands[i]; break; }
+        p.ks = 1;
+        uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
+        if (st < 2) st = 2;
+        p.stages = st < num_kb ? st : (num_kb ? num_kb : 1);
+        return p;
+    }
+    uint32_t best_kb = 0xffffffffu, best_ctas = 0;
+    p = GemmPlan{16, 1, 1, 1};
+    const uint32_t bns[3] = {16, 32, 64};
+    const uint32_t kss[4] = {1, 2, 4, 8};
+    for (int bi = 0; bi < 3; bi++)
+        for (int ki = 0; ki < 4; ki++) {
+            const uint32_t bn = bns[bi], ks = kss[ki];
+            if (ks > 1 && (!allow_split || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
+            const uint32_t per = cdiv(num_kb, ks);
+            if (ks > 1 && (ks - 1) * per >= num_kb) continue;  // every CTA of the cluster gets work
+            const uint32_t ctas = cdiv(n, bn) * ks;
+            if (ctas > slots && !(bi == 2 && ki == 0)) continue;
+            const bool better = per < best_kb || (per == best_kb && ctas > best_ctas);
+            if (better) { best_kb = per; best_ctas = ctas; p.bn = bn; p.ks = ks; }
+        }
+    const uint32_t per = cdiv(num_kb, p.ks);
+    const uint32_t red = p.ks > 1 ? GB_M * p.bn * 4 : 0;
+    uint32_t st = (SMEM_TWO_PER_SM - 1024 - red) / stage_bytes(p.bn);
+    if (st > G_MAX_STAGES) st = G_MAX_STAGES;
+    if (st < 2) st = 2;
+    p.stages = st < per ? st : (per ? per : 1);
+    return p;
 }
 
 template <int BN, int EPI>
-static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap& tmB, void* c, uint32_t m, uint32_t n,
-                      uint32_t k, uint32_t ldc) {
+static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpi& ep, uint32_t m, uint32_t n,
+                      uint32_t k, const GemmPlan& p) {
     using C = GemmCfg<BN>;
-    static bool attr_set[64] = {};
+    const size_t smem = (size_t)p.stages * C::STAGE_BYTES + (p.ks > 1 ? C::RED_BYTES : 0) + 1024;
+    static size_t attr_set[64] = {};
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
-    if (!attr_set[dev & 63]) {
-        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_set[dev & 63] = true;
+    if (attr_set[dev & 63] < smem) {
+        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+        attr_set[dev & 63] = SMEM_ONE_PER_SM;
     }
-    dim3 grid(cdiv(n, BN), cdiv(m, GB_M));
-    gemm_bf16_kernel<BN, EPI><<<grid, G_THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, c, m, n, k, ldc);
-    AK_COUNT_LAUNCH();
-    AK_CHECK_LAUNCH();
-    return AK_OK;
+    uint32_t need = p.kseg * BN, cols = 32;
+    while (cols < need) cols *= 2;
+    AK_REQUIRE(cols <= 512, AK_ERR_UNSUPPORTED, "gemm_bf16: %u accumulator columns exceed TMEM", need);
+    return launch_k(gemm_bf16_kernel<BN, EPI>, dim3(cdiv(n, BN), cdiv(m, GB_M), p.ks), dim3(G_THREADS), smem, st, dim3(1, 1, p.ks),
+                    tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols);
 }
 
 template <int BN>
-static int launch_bn(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k,
-                     uint32_t epi, uint32_t ldc) {
+static int launch_bn(cudaStream_t st, const void* a, const void* wt, const GemmEpi& ep, uint32_t m, uint32_t n, uint32_t k,
+                     uint32_t epi, const GemmPlan& p) {
     CUtensorMap tmA, tmB;
     int rc = make_tmap_2d(&tmA, a, 2, k, m, (uint64_t)k * 2, GB_K, GB_M, TMA_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, wt, 2, k, n, (uint64_t)k * 2, GB_K, BN, TMA_SWIZZLE_128B);
     if (rc) return rc;
     switch (epi) {
-        case AK_EPI_STORE_F32: return launch_cfg<BN, AK_EPI_STORE_F32>(st, tmA, tmB, c, m, n, k, ldc);
-        case AK_EPI_ADD_F32: return launch_cfg<BN, AK_EPI_ADD_F32>(st, tmA, tmB, c, m, n, k, ldc);
-        case AK_EPI_STORE_BF16: return launch_cfg<BN, AK_EPI_STORE_BF16>(st, tmA, tmB, c, m, n, k, ldc);
-        case AK_EPI_SILU_BF16: return launch_cfg<BN, AK_EPI_SILU_BF16>(st, tmA, tmB, c, m, n, k, ldc);
+        case AK_EPI_STORE_F32: return launch_cfg<BN, AK_EPI_STORE_F32>(st, tmA, tmB, ep, m, n, k, p);
+        case AK_EPI_ADD_F32: return launch_cfg<BN, AK_EPI_ADD_F32>(st, tmA, tmB, ep, m, n, k, p);
+        case AK_EPI_STORE_BF16: return launch_cfg<BN, AK_EPI_STORE_BF16>(st, tmA, tmB, ep, m, n, k, p);
+        case AK_EPI_SILU_BF16: return launch_cfg<BN, AK_EPI_SILU_BF16>(st, tmA, tmB, ep, m, n, k, p);
+        case EPI_ARGMAX: return launch_cfg<BN, EPI_ARGMAX>(st, tmA, tmB, ep, m, n, k, p);
+        case EPI_STORE_F32_ARGMAX: return launch_cfg<BN, EPI_STORE_F32_ARGMAX>(st, tmA, tmB, ep, m, n, k, p);
     }
     set_error("gemm_bf16: unknown epilogue %u", epi);
     return AK_ERR_INVALID_ARG;
 }
 
-// Tile width: the narrowest N tile that still gives about one wave of CTAs keeps the weight
-// stream spread over all SMs for small m (decode), wide tiles amortise the A tile for large m.
-static uint32_t pick_bn(uint32_t m, uint32_t n) {
-    const uint32_t mt = cdiv(m, GB_M);
-    const uint32_t cands[5] = {256, 128, 64, 32, 16};
-    for (int i = 0; i < 5; i++) {
-        uint32_t bn = cands[i];
-        if ((uint64_t)mt * cdiv(n, bn) >= 148) return bn;
+static int launch_planned(cudaStream_t st, const void* a, const void* wt, const GemmEpi& ep, uint32_t m, uint32_t n, uint32_t k,
+                          uint32_t epi, const GemmPlan& p) {
+    switch (p.bn) {
+        case 256: return launch_bn<256>(st, a, wt, ep, m, n, k, epi, p);
+        case 176: return launch_bn<176>(st, a, wt, ep, m, n, k, epi, p);
+        case 128: return launch_bn<128>(st, a, wt, ep, m, n, k, epi, p);
+        case 64: return launch_bn<64>(st, a, wt, ep, m, n, k, epi, p);
+        case 32: return launch_bn<32>(st, a, wt, ep, m, n, k, epi, p);
+        default: return launch_bn<16>(st, a, wt, ep, m, n, k, epi, p);
     }
-    return 16;
+}
+
+static int check_operands(const void* a, const void* wt, uint32_t k) {
+    AK_REQUIRE(k >= 8 && k % 8 == 0, AK_ERR_UNSUPPORTED, "gemm_bf16: k (%u) must be a positive multiple of 8", k);
+    AK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)wt % 16) == 0, AK_ERR_INVALID_ARG, "gemm_bf16: operands must be 16-byte aligned");
+    return AK_OK;
 }
 
 int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k,
-                     uint32_t epilogue, uint32_t ldc) {
+                     uint32_t epilogue, uint32_t ldc, bool invariant) {
     if (m == 0 || n == 0) return AK_OK;
-    AK_REQUIRE(k >= 8 && k % 8 == 0, AK_ERR_UNSUPPORTED, "gemm_bf16: k (%u) must be a positive multiple of 8", k);
-    AK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)wt % 16) == 0 && ((uintptr_t)c % 16) == 0, AK_ERR_INVALID_ARG,
-               "gemm_bf16: operands must be 16-byte aligned");
-    if (ldc == 0) ldc = n;
-    switch (pick_bn(m, n)) {
-        case 256: return launch_bn<256>(st, a, wt, c, m, n, k, epilogue, ldc);
-        case 128: return launch_bn<128>(st, a, wt, c, m, n, k, epilogue, ldc);
-        case 64: return launch_bn<64>(st, a, wt, c, m, n, k, epilogue, ldc);
-        case 32: return launch_bn<32>(st, a, wt, c, m, n, k, epilogue, ldc);
-        default: return launch_bn<16>(st, a, wt, c, m, n, k, epilogue, ldc);
-    }
+    int rc = check_operands(a, wt, k);
+    if (rc) return rc;
+    AK_REQUIRE(epilogue <= AK_EPI_SILU_BF16, AK_ERR_INVALID_ARG, "gemm_bf16: unknown epilogue %u", epilogue);
+    AK_REQUIRE(((uintptr_t)c % 16) == 0, AK_ERR_INVALID_ARG, "gemm_bf16: output must be 16-byte aligned");
+    GemmEpi ep{};
+    ep.c = c;
+    ep.ldc = ldc ? ldc : n;
+    // the split-K exchange stores 4-column groups: it needs 4-aligned rows
+    const bool allow_split = (ep.ldc % 4) == 0;
+    return launch_planned(st, a, wt, ep, m, n, k, epilogue, plan_gemm(m, n, k, allow_split, invariant));
+}
+
+uint32_t gemm_argmax_tiles(uint32_t m, uint32_t n, uint32_t k) { return cdiv(n, plan_gemm(m, n, k, false).bn); }
+
+// logits (optional, f32 [m, ldc]) and per-tile row maxima; a second tiny kernel finishes the argmax.
+int launch_gemm_bf16_argmax(cudaStream_t st, const void* a, const void* wt, float* logits, uint32_t ldc, float* part_val,
+                            uint32_t* part_idx, uint32_t m, uint32_t n, uint32_t k) {
+    if (m == 0 || n == 0) return AK_OK;
+    int rc = check_operands(a, wt, k);
+    if (rc) return rc;
+    GemmPlan p = plan_gemm(m, n, k, false);
+    p.ks = 1;
+    GemmEpi ep{};
+    ep.c = logits;
+    ep.ldc = ldc ? ldc : n;
+    ep.amax_val = part_val;
+    ep.amax_idx = part_idx;
+    ep.amax_ld = cdiv(n, p.bn);
+    return launch_planned(st, a, wt, ep, m, n, k, logits ? EPI_STORE_F32_ARGMAX : EPI_ARGMAX, p);
 }
 
 int gemm_bf16_check_status(cudaStream_t st) {
@@ -301,5 +536,5 @@ int gemm_bf16_check_status(cudaStream_t st) {
 using namespace ak;
 extern "C" int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue) {
     AK_REQUIRE(a && wt && c, AK_ERR_INVALID_ARG, "ak_gemm_bf16: null pointer");
-    return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, m.n);
+    return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, m.n, false);
 }

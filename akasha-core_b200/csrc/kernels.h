@@ -46,9 +46,20 @@ int launch_gemm_f32(cudaStream_t st, const float* a, const float* b, float* c, u
                     uint32_t k, uint32_t flags);
 
 // ---- gemm_tcgen05.cu (bf16 tensor cores) --------------------------------------------------------
+// invariant: keep the K summation structure a function of (n, k) only, so a row's result is the
+// same whether 1 or 10,000 rows share the launch (the engine's batch invariance); costs some
+// throughput for m > 128. false = fastest plan for the given m.
 int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n,
-                     uint32_t k, uint32_t epilogue, uint32_t ldc);
+                     uint32_t k, uint32_t epilogue, uint32_t ldc, bool invariant);
 int gemm_bf16_check_status(cudaStream_t st);  // reads the device status word (syncs the stream)
+// lm_head with the greedy argmax fused into the epilogue: every N tile writes each row's
+// (max, first index) to part_val/part_idx [m][gemm_argmax_tiles()]; launch_argmax_finish reduces
+// them (lowest index wins ties). logits may be NULL (nothing but the partials is written).
+uint32_t gemm_argmax_tiles(uint32_t m, uint32_t n, uint32_t k);
+int launch_gemm_bf16_argmax(cudaStream_t st, const void* a, const void* wt, float* logits, uint32_t ldc, float* part_val,
+                            uint32_t* part_idx, uint32_t m, uint32_t n, uint32_t k);
+int launch_argmax_finish(cudaStream_t st, const float* part_val, const uint32_t* part_idx, uint32_t rows, uint32_t tiles,
+                         const int32_t* row_active, uint32_t* out_idx);
 
 // ---- attn_decode.cu ----------------------------------------------------------------------------
 size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t n_splits);

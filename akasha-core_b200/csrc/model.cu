@@ -185,6 +185,7 @@ Runner::~Runner() {
     for (void* p : k_pool_) cudaFree(p);
     for (void* p : v_pool_) cudaFree(p);
     cudaFree(hidden_); cudaFree(xn_); cudaFree(qkv_); cudaFree(qbuf_); cudaFree(attn_); cudaFree(up_);
+    cudaFree(amax_val_); cudaFree(amax_idx_);
     cudaFree(xf_); cudaFree(logits_); cudaFree(attn_scratch_); cudaFree(rope_table_);
     cudaFree(d_desc_); cudaFree(d_sampled_);
     if (h_desc_) cudaFreeHost(h_desc_);
@@ -238,14 +239,20 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaMalloc(&attn_, R * D * act));
     AK_CUDA(cudaMalloc(&up_, R * F * act));
     AK_CUDA(cudaMalloc(&xf_, (size_t)max_seqs * D * act));
-    AK_CUDA(cudaMalloc((void**)&logits_, (size_t)max_seqs * V * 4));
+    logits_ld_ = (w->dtype == AK_BF16) ? (V + 3) / 4 * 4 : V;
+    AK_CUDA(cudaMalloc((void**)&logits_, (size_t)max_seqs * logits_ld_ * 4));
+    if (w->dtype == AK_BF16) {
+        amax_tiles_ = gemm_argmax_tiles(max_seqs, V, D);
+        AK_CUDA(cudaMalloc((void**)&amax_val_, (size_t)max_seqs * amax_tiles_ * 4));
+        AK_CUDA(cudaMalloc((void**)&amax_idx_, (size_t)max_seqs * amax_tiles_ * 4));
+    }
     AK_CUDA(cudaMemsetAsync(hidden_, 0, R * D * 4, ctx->stream));
     AK_CUDA(cudaMemsetAsync(xn_, 0, R * D * act, ctx->stream));
     AK_CUDA(cudaMemsetAsync(qkv_, 0, R * 3 * D * 4, ctx->stream));
     AK_CUDA(cudaMemsetAsync(qbuf_, 0, R * D * act, ctx->stream));
     AK_CUDA(cudaMemsetAsync(attn_, 0, R * D * act, ctx->stream));
     AK_CUDA(cudaMemsetAsync(up_, 0, R * F * act, ctx->stream));
-    AK_CUDA(cudaMemsetAsync(logits_, 0, (size_t)max_seqs * V * 4, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(logits_, 0, (size_t)max_seqs * logits_ld_ * 4, ctx->stream));
     attn_scratch_bytes_ = attn_decode_scratch_bytes(max_seqs, H, hd, 32);
     AK_CUDA(cudaMalloc((void**)&attn_scratch_, attn_scratch_bytes_));
 
@@ -275,7 +282,7 @@ int Runner::gemm(const void* a, const void* wt, void* c, uint32_t m, uint32_t n,
         return launch_gemm_f32(st, (const float*)a, (const float*)wt, (float*)c, m, n, k, flags);
     }
     uint32_t epi = mode == 1 ? AK_EPI_ADD_F32 : (mode == 2 ? AK_EPI_SILU_BF16 : AK_EPI_STORE_F32);
-    return launch_gemm_bf16(st, a, wt, c, m, n, k, epi, n);
+    return launch_gemm_bf16(st, a, wt, c, m, n, k, epi, n, true);
 }
 
 int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode,
@@ -320,8 +327,14 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
         RC(gemm(up_, b.down, hidden_, T, D, F, 1));
     }
     RC(launch_rmsnorm(st, hidden_, w_->final_norm, xf_, dt, d_desc_ + d_.out_rows, max_seqs_, D, c.norm_eps));
-    RC(gemm(xf_, w_->lm_head, logits_, max_seqs_, V, D, 0));
-    RC(launch_argmax(st, logits_, max_seqs_, V, V, d_desc_ + d_.out_rows, d_sampled_));
+    if (dt == AK_BF16) {
+        // greedy argmax fused into the lm_head epilogue: logits are written only when someone reads them
+        RC(launch_gemm_bf16_argmax(st, xf_, w_->lm_head, keep_logits_ ? logits_ : nullptr, logits_ld_, amax_val_, amax_idx_, max_seqs_, V, D));
+        RC(launch_argmax_finish(st, amax_val_, amax_idx_, max_seqs_, amax_tiles_, d_desc_ + d_.out_rows, d_sampled_));
+    } else {
+        RC(gemm(xf_, w_->lm_head, logits_, max_seqs_, V, D, 0));
+        RC(launch_argmax(st, logits_, max_seqs_, V, V, d_desc_ + d_.out_rows, d_sampled_));
+    }
 #undef RC
     (void)n_pf_rows;
     return AK_OK;
@@ -403,7 +416,7 @@ float Runner::last_attn_ms() {
 
 int Runner::read_logits(uint32_t slot, float* host_out) {
     const uint32_t V = w_->cfg.vocab_size;
-    AK_CUDA(cudaMemcpyAsync(host_out, logits_ + (size_t)slot * V, (size_t)V * 4, cudaMemcpyDeviceToHost, ctx_->stream));
+    AK_CUDA(cudaMemcpyAsync(host_out, logits_ + (size_t)slot * logits_ld_, (size_t)V * 4, cudaMemcpyDeviceToHost, ctx_->stream));
     AK_CUDA(cudaStreamSynchronize(ctx_->stream));
     return AK_OK;
 }

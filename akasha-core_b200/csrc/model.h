@@ -85,6 +85,7 @@ class Runner {
     uint32_t max_prefill_tokens() const { return max_pf_tokens_; }
     uint32_t dtype() const { return w_->dtype; }
     void enable_attn_timing(bool on) { attn_timing_ = on; }
+    void set_keep_logits(bool on) { keep_logits_ = on; }
     float last_attn_ms();
     uint64_t graph_launches = 0, eager_steps = 0;
     uint64_t h2d_bytes = 0, d2h_bytes = 0;   // bytes copied by run() / run_decode_graph()
@@ -111,6 +112,11 @@ class Runner {
     void* up_ = nullptr;
     void* xf_ = nullptr;
     float* logits_ = nullptr;
+    uint32_t logits_ld_ = 0;          // row pitch of logits_ (padded to 4 in bf16 mode)
+    bool keep_logits_ = true;         // false: the engine never reads logits, only the argmax
+    float* amax_val_ = nullptr;       // per-tile row maxima of the lm_head (bf16 mode)
+    uint32_t* amax_idx_ = nullptr;
+    uint32_t amax_tiles_ = 0;
     float* attn_scratch_ = nullptr;
     size_t attn_scratch_bytes_ = 0;
     float2* rope_table_ = nullptr;

@@ -1,6 +1,7 @@
 // Host-side plumbing: thread-local error text, device/stream/memory helpers of the C ABI,
 // and TMA tensor-map construction.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "kernels.h"
@@ -10,6 +11,16 @@ namespace ak {
 
 static thread_local char g_err[512] = "";
 thread_local unsigned long long g_launch_count = 0;
+
+bool pdl_enabled() {
+    // AK_PDL=0 in the environment turns programmatic dependent launch off (for A/B timing)
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("AK_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
 
 void set_error(const char* fmt, ...) {
     va_list ap;

@@ -150,7 +150,7 @@ def bf16_round(orc, a):
     return orc.round_bf16(np.ascontiguousarray(a, np.float32))
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (1, 768, 768), (64, 768, 3072), (7, 50257, 768), (128, 256, 64),
+@pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (1, 768, 768), (64, 768, 3072), (7, 50257, 768), (128, 256, 64), (64, 3072, 768), (64, 8192, 2048), (100, 2048, 8192), (3, 40, 1024),
                                    (300, 520, 200), (1000, 3072, 768), (129, 24, 8), (64, 6144, 2048)])
 def test_gemm_bf16_store_f32(ak, orc, torch_cuda, m, n, k):
     torch = torch_cuda

@@ -298,3 +298,32 @@ def test_engine_capacity_and_errors(ak, ctx):
     with pytest.raises(ak.AkashaError):
         e.poll(ids[0])
     e.close(); w.close()
+
+
+def test_session_bf16_fused_argmax_and_oracle_logits(ak, orc, ctx):
+    """bf16 mode: the argmax fused into the lm_head epilogue equals the first maximum of the logits
+    the same launch stored, and the logits track the oracle's bf16-emulating mode."""
+    cfg = ak.ModelConfig(5003, 256, 4, 2, 128)   # vocab not a multiple of any tile width
+    params = ak.synthetic_weights(cfg, seed=11, std=0.05)
+    w = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_BF16)
+    prompt = ak.uniform_tokens(37, cfg.vocab_size, seed=5)
+    s = ak.InferenceSession(ctx, w, 128)
+    s.replace_cache()
+    logits, tok = s.prefill(prompt)
+    toks, all_logits = [tok], [logits]
+    for _ in range(20):
+        logits, tok = s.decode_step(toks[-1])
+        toks.append(tok)
+        all_logits.append(logits)
+    assert all(int(np.argmax(l)) == t for l, t in zip(all_logits, toks))
+    rparams = [p if p.ndim == 1 else orc.round_bf16(p) for p in params]
+    om = orc.Model(cfg.as_dict(), rparams, act_bf16=True)
+    os_ = orc.Session(om, 128)
+    rc, ol = os_.prefill(prompt)
+    errs = [float(np.max(np.abs(all_logits[0] - ol)))]
+    for i, t in enumerate(toks[:-1]):     # teacher-forced with the GPU's tokens
+        rc, ol = os_.decode_step(int(t))
+        errs.append(float(np.max(np.abs(all_logits[i + 1] - ol))))
+    print(f"bf16 session vs bf16-emulating oracle: max |dlogit| {max(errs):.3e}")
+    assert max(errs) < 5e-2
+    s.close(); w.close()
