@@ -327,3 +327,36 @@ def test_session_bf16_fused_argmax_and_oracle_logits(ak, orc, ctx):
     print(f"bf16 session vs bf16-emulating oracle: max |dlogit| {max(errs):.3e}")
     assert max(errs) < 5e-2
     s.close(); w.close()
+
+
+# ---- the 162M config-2 case: 512-token prefill + 384 greedy steps (max_ctx 1024), fp32 parity ----
+def test_akasha_hall_config2_parity(ak, orc, ctx):
+    cfg = ak.ModelConfig.akasha_hall_1()
+    params = ak.synthetic_weights(cfg, seed=0, std=0.02)
+    w = ak.ModelWeights.from_params(ctx, cfg, params, ak.AK_F32)
+    prompt = ak.uniform_tokens(512, cfg.vocab_size, seed=1)
+    steps, max_ctx = 384, 1024    # the session's context is a parameter independent of cfg.seq_len
+    s = ak.InferenceSession(ctx, w, max_ctx)
+    s.replace_cache()
+    logits, tok = s.prefill(prompt)
+    toks, all_logits = [tok], [logits]
+    for _ in range(steps - 1):
+        logits, tok = s.decode_step(toks[-1])
+        toks.append(tok)
+        all_logits.append(logits)
+    om = orc.Model(cfg.as_dict(), params)
+    os_ = orc.Session(om, max_ctx)
+    st, want, ol = os_.generate_greedy(prompt, steps, want_logits=True)
+    errs = [float(np.max(np.abs(a - b))) for a, b in zip(all_logits, ol)]
+    margins = [float(np.diff(np.partition(l, -2)[-2:])[0]) for l in ol[:steps]]
+    print(f"config-2: max |dlogit| {max(errs):.3e}, min top-2 margin {min(margins):.3e}")
+    assert list(want) == toks
+    assert max(errs) < LOGIT_TOL
+    # KV slot indexing: position p of every layer sits in row p, K post-RoPE, V raw
+    for layer in (0, cfg.num_layers - 1):
+        gk, gv = s.read_cache(layer)
+        ok, ov = os_.cache(layer)
+        n = s.cur_len
+        assert n == 512 + steps - 1
+        assert np.max(np.abs(gk - ok[:n])) < 1e-3 and np.max(np.abs(gv - ov[:n])) < 1e-3
+    s.close(); w.close()
