@@ -17,6 +17,8 @@
 #include "kernels.h"
 #include "tma.h"
 
+#include <stdlib.h>
+
 namespace ak {
 
 __device__ unsigned int g_attn_decode_status = 0;
@@ -24,7 +26,7 @@ __device__ unsigned int g_attn_decode_status = 0;
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_BS = 16;  // positions per KV block
 
-template <typename T, int HD> struct DecCfg {
+template <typename T, int HD, int ST> struct DecCfg {
     static constexpr int GROUPS = HD * (int)sizeof(T) / 128;   // 128-byte column groups per row
     static constexpr int EPC = 16 / (int)sizeof(T);            // elements per 16-byte chunk
     static constexpr int EPG = 128 / (int)sizeof(T);           // elements per column group
@@ -32,7 +34,7 @@ template <typename T, int HD> struct DecCfg {
     static constexpr int EPL = HD / 32;                        // output dims per lane
     static constexpr int TILE_BYTES = DEC_BS * HD * (int)sizeof(T);  // one K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
-    static constexpr int STAGES = (STAGE_BYTES <= 4096) ? 4 : (STAGE_BYTES <= 8192 ? 3 : 2);
+    static constexpr int STAGES = ST;   // ring depth per warp
     static constexpr int SMEM_BYTES = DEC_WARPS * STAGES * STAGE_BYTES + 1024;  // + alignment slack
 };
 
@@ -56,7 +58,7 @@ template <> __device__ __forceinline__ void unpack16<bf16>(const uint4& raw, flo
     out[6] = __uint_as_float(raw.w << 16); out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
-template <typename T, int HD>
+template <typename T, int HD, int ST>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const T* __restrict__ q, const int32_t* __restrict__ block_tables,
@@ -64,7 +66,7 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                          uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits) {
     pdl_wait();
     pdl_trigger();
-    using C = DecCfg<T, HD>;
+    using C = DecCfg<T, HD, ST>;
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[DEC_WARPS][C::STAGES];
     __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
@@ -361,11 +363,11 @@ uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t max_kv_
     return want < 1 ? 1 : want;
 }
 
-template <typename T, int HD>
-static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+template <typename T, int HD, int ST>
+static int launch_fast_st(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                        const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
                        const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
-    using C = DecCfg<T, HD>;
+    using C = DecCfg<T, HD, ST>;
     CUtensorMap tmK, tmV;
     int rc = make_tmap_2d(&tmK, k_pool, sizeof(T), HD, pool_rows, (uint64_t)HD * sizeof(T), C::EPG, DEC_BS, TMA_SWIZZLE_128B);
     if (rc) return rc;
@@ -375,17 +377,37 @@ static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        AK_CUDA(cudaFuncSetAttribute(attn_decode_paged_kernel<T, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        AK_CUDA(cudaFuncSetAttribute(attn_decode_paged_kernel<T, HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         attr_set[dev & 63] = true;
     }
     dim3 grid(p.heads, p.rows, n_splits);
-    AK_TRY(launch_k(attn_decode_paged_kernel<T, HD>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, 
+    AK_TRY(launch_k(attn_decode_paged_kernel<T, HD, ST>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, 
         tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits));
     if (n_splits > 1) {
         dim3 g2(p.heads, p.rows);
         AK_TRY(launch_k(attn_decode_combine_kernel<T, HD>, dim3(g2), dim3(32), 0, st, NO_CLUSTER, (const float*)scratch, (T*)out, p.heads, n_splits));
     }
     return AK_OK;
+}
+
+// Ring depth: a 2-deep ring per warp keeps a CTA at 33 KB (bf16, head_dim 64), so 6 CTAs = 24
+// warps share an SM and a 64-sequence decode batch is resident in ONE wave. More resident warps
+// hide latency better than a deeper ring per warp. AK_ATTN_STAGES overrides (tuning).
+template <typename T, int HD>
+static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+                       const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                       const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
+    constexpr int STAGE_BYTES = 2 * DEC_BS * HD * (int)sizeof(T);
+    constexpr int DEEP = (STAGE_BYTES <= 4096) ? 4 : (STAGE_BYTES <= 8192 ? 3 : 2);
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("AK_ATTN_STAGES");
+        forced = e ? atoi(e) : 0;
+    }
+    int want = 2;  // measured: 6 CTAs/SM x 2 stages beats 3 CTAs/SM x 4 stages at 64 and at 1024 sequences
+    if (forced == 2 || forced == DEEP) want = forced;
+    if (want == 2) return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
+    return launch_fast_st<T, HD, DEEP>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
 }
 
 // Rows of the 2-D view [n_blocks*heads*16, head_dim] of a pool. With pool_blocks given, a block

@@ -7,13 +7,17 @@
 
 namespace ak {
 
-constexpr int PF_BQ = 64, PF_BK = 64, PF_THREADS = 256, PF_BS = 16;
+constexpr int PF_BK = 64, PF_THREADS = 256, PF_BS = 16;
 
-template <typename T, int HD> struct PfSmem {
-    float qt[HD][PF_BQ + 4];   // Q^T
+// RPT = query rows per thread: the query tile is 16*RPT rows. RPT = 4 (64-row tiles) has the best
+// FMA-to-shared-load ratio; RPT = 1 (16-row tiles) makes four times as many CTAs, which is what a
+// single short prompt joining a decode batch needs to occupy the machine.
+template <typename T, int HD, int RPT> struct PfSmem {
+    static constexpr int BQ = 16 * RPT;
+    float qt[HD][BQ + 4];   // Q^T
     float kt[HD][PF_BK + 4];   // K^T
     float vs[PF_BK][HD + 4];   // V
-    float pt[PF_BK][PF_BQ + 4];  // P^T
+    float pt[PF_BK][BQ + 4];  // P^T
 };
 
 template <typename T> __device__ __forceinline__ void load_chunk(const T* src, float* out);
@@ -30,7 +34,7 @@ template <> __device__ __forceinline__ void load_chunk<bf16>(const bf16* src, fl
 }
 
 // grid: (q tiles, heads, sequences). PAGED: k/v are pools + block table; else contiguous rows.
-template <typename T, int HD, bool PAGED>
+template <typename T, int HD, bool PAGED, int RPT>
 __global__ void __launch_bounds__(PF_THREADS)
 attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const T* __restrict__ vbase,
                     const int32_t* __restrict__ block_tables, uint32_t max_blocks, const int32_t* __restrict__ cu,
@@ -42,7 +46,8 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
     constexpr int CPR = HD / EPC;      // 16-byte chunks per row
     constexpr int OC = HD / 16;        // output columns per thread
     extern __shared__ uint8_t smem_raw[];
-    PfSmem<T, HD>& sm = *reinterpret_cast<PfSmem<T, HD>*>(smem_raw);
+    constexpr int PF_BQ = 16 * RPT;
+    PfSmem<T, HD, RPT>& sm = *reinterpret_cast<PfSmem<T, HD, RPT>*>(smem_raw);
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, qtile = blockIdx.x;
     const uint32_t dim = heads * HD;
@@ -66,9 +71,9 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
         for (int i = 0; i < EPC; i++) sm.qt[c * EPC + i][r] = v[i];
     }
 
-    float m_run[4], l_run[4], o[4][OC];
+    float m_run[RPT], l_run[RPT], o[RPT][OC];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < RPT; i++) {
         m_run[i] = -INFINITY; l_run[i] = 0.0f;
 #pragma unroll
         for (int c = 0; c < OC; c++) o[i][c] = 0.0f;
@@ -112,26 +117,28 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
         }
         __syncthreads();
 
-        // ---- S = Q K^T for rows 4ty..4ty+3, keys 4tx..4tx+3
-        float s[4][4];
+        // ---- S = Q K^T for rows RPT*ty..RPT*ty+RPT-1, keys 4tx..4tx+3
+        float s[RPT][4];
 #pragma unroll
-        for (int i = 0; i < 4; i++)
+        for (int i = 0; i < RPT; i++)
 #pragma unroll
             for (int j = 0; j < 4; j++) s[i][j] = 0.0f;
 #pragma unroll 8
         for (int d = 0; d < HD; d++) {
-            float4 qa = *reinterpret_cast<const float4*>(&sm.qt[d][ty * 4]);
-            float4 kb = *reinterpret_cast<const float4*>(&sm.kt[d][tx * 4]);
-            float qa_[4] = {qa.x, qa.y, qa.z, qa.w}, kb_[4] = {kb.x, kb.y, kb.z, kb.w};
+            float qa_[RPT];
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int i = 0; i < RPT; i++) qa_[i] = sm.qt[d][ty * RPT + i];
+            float4 kb = *reinterpret_cast<const float4*>(&sm.kt[d][tx * 4]);
+            float kb_[4] = {kb.x, kb.y, kb.z, kb.w};
+#pragma unroll
+            for (int i = 0; i < RPT; i++)
 #pragma unroll
                 for (int j = 0; j < 4; j++) s[i][j] = fmaf(qa_[i], kb_[j], s[i][j]);
         }
         // ---- mask, online softmax (16 lanes share a row group)
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            uint32_t qi = q0 + ty * 4 + i;
+        for (int i = 0; i < RPT; i++) {
+            uint32_t qi = q0 + ty * RPT + i;
             float mx = -INFINITY;
 #pragma unroll
             for (int j = 0; j < 4; j++) {
@@ -160,13 +167,15 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
         // ---- P^T to shared
 #pragma unroll
         for (int j = 0; j < 4; j++)
-            *reinterpret_cast<float4*>(&sm.pt[tx * 4 + j][ty * 4]) = make_float4(s[0][j], s[1][j], s[2][j], s[3][j]);
+#pragma unroll
+            for (int i = 0; i < RPT; i++) sm.pt[tx * 4 + j][ty * RPT + i] = s[i][j];
         __syncthreads();
         // ---- O += P V, thread owns rows 4ty..+3 and columns tx*OC..+OC-1
 #pragma unroll 4
         for (int j = 0; j < PF_BK; j++) {
-            float4 pa = *reinterpret_cast<const float4*>(&sm.pt[j][ty * 4]);
-            float pa_[4] = {pa.x, pa.y, pa.z, pa.w};
+            float pa_[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; i++) pa_[i] = sm.pt[j][ty * RPT + i];
             float vv[OC];
 #pragma unroll
             for (int c = 0; c < OC; c += 4) {
@@ -174,15 +183,15 @@ attn_prefill_kernel(const T* __restrict__ q, const T* __restrict__ kbase, const 
                 vv[c] = t.x; vv[c + 1] = t.y; vv[c + 2] = t.z; vv[c + 3] = t.w;
             }
 #pragma unroll
-            for (int i = 0; i < 4; i++)
+            for (int i = 0; i < RPT; i++)
 #pragma unroll
                 for (int c = 0; c < OC; c++) o[i][c] = fmaf(pa_[i], vv[c], o[i][c]);
         }
     }
     // ---- write
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        uint32_t qi = q0 + ty * 4 + i;
+    for (int i = 0; i < RPT; i++) {
+        uint32_t qi = q0 + ty * RPT + i;
         if (qi >= len) continue;
         float inv = 1.0f / l_run[i];
         T* dst = out + (size_t)(row0 + qi) * dim + (size_t)h * HD + tx * OC;
@@ -243,22 +252,34 @@ __global__ void attn_prefill_generic_kernel(const T* __restrict__ q, const T* __
     if (l_cache && lane == 0) l_cache[(size_t)qi * heads + h] = mx + logf(sum);
 }
 
-template <typename T, int HD, bool PAGED>
-static int launch_tiled(cudaStream_t st, const T* q, const T* k, const T* v, const int32_t* bt, uint32_t max_blocks,
-                        const int32_t* cu, const int32_t* seq_slot, T* out, float* l_cache, uint32_t n_seqs,
-                        uint32_t max_len, uint32_t row_base, uint32_t heads, float scale, uint32_t fixed_len) {
-    size_t smem = sizeof(PfSmem<T, HD>);
+template <typename T, int HD, bool PAGED, int RPT>
+static int launch_tiled_rpt(cudaStream_t st, const T* q, const T* k, const T* v, const int32_t* bt, uint32_t max_blocks,
+                            const int32_t* cu, const int32_t* seq_slot, T* out, float* l_cache, uint32_t n_seqs,
+                            uint32_t max_len, uint32_t row_base, uint32_t heads, float scale, uint32_t fixed_len) {
+    constexpr int PF_BQ = 16 * RPT;
+    size_t smem = sizeof(PfSmem<T, HD, RPT>);
     static bool attr_set[64] = {};
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        AK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<T, HD, PAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        AK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<T, HD, PAGED, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev & 63] = true;
     }
     dim3 grid(cdiv(max_len, PF_BQ), heads, n_seqs);
-    AK_TRY(launch_k(attn_prefill_kernel<T, HD, PAGED>, dim3(grid), dim3(PF_THREADS), smem, st, NO_CLUSTER, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache,
+    AK_TRY(launch_k(attn_prefill_kernel<T, HD, PAGED, RPT>, dim3(grid), dim3(PF_THREADS), smem, st, NO_CLUSTER, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache,
                                                                        row_base, heads, scale, fixed_len));
     return AK_OK;
+}
+
+template <typename T, int HD, bool PAGED>
+static int launch_tiled(cudaStream_t st, const T* q, const T* k, const T* v, const int32_t* bt, uint32_t max_blocks,
+                        const int32_t* cu, const int32_t* seq_slot, T* out, float* l_cache, uint32_t n_seqs,
+                        uint32_t max_len, uint32_t row_base, uint32_t heads, float scale, uint32_t fixed_len) {
+    // 64-row query tiles when they already give two waves of CTAs, else 16-row tiles
+    const uint64_t big = (uint64_t)cdiv(max_len, 64) * heads * n_seqs;
+    if (big >= 296)
+        return launch_tiled_rpt<T, HD, PAGED, 4>(st, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache, n_seqs, max_len, row_base, heads, scale, fixed_len);
+    return launch_tiled_rpt<T, HD, PAGED, 1>(st, q, k, v, bt, max_blocks, cu, seq_slot, out, l_cache, n_seqs, max_len, row_base, heads, scale, fixed_len);
 }
 
 template <typename T, bool PAGED>

@@ -201,8 +201,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
 
     // 4. launch
     int rc;
-    const bool graph = e->cfg.use_cuda_graph && admitted.empty();
-    if (graph) rc = r.run_decode_graph(max_kv);
+    const bool graph = e->cfg.use_cuda_graph != 0;
+    if (graph) rc = r.run_graph(pf_rows, (uint32_t)admitted.size(), max_pf);
     else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
     if (rc) return rc;
     rc = r.sync();

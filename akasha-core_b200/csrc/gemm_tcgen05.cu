@@ -207,15 +207,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sm;
-    // everything above touched only this CTA's shared memory and TMEM; from here on global memory
-    // written by the preceding kernels is read
-    pdl_wait();
+    // Everything above touched only this CTA's shared memory and TMEM. Let the next kernel's blocks
+    // be scheduled as SMs free up; they, like this one, wait for their prerequisite grid before
+    // touching anything it wrote.
     pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer
         if (lane == 0) {
-            for (uint32_t i = 0; i < num_kb; i++) {
+            // The weight tiles do not depend on the preceding kernel: the first ring of them is
+            // requested BEFORE waiting for it, so the weight stream from HBM overlaps the
+            // predecessor's tail. The activation tiles follow after the wait.
+            const uint32_t pre = num_kb < stages ? num_kb : stages;
+            for (uint32_t i = 0; i < pre; i++) {
+                uint8_t* b_dst = smem + (size_t)i * C::STAGE_BYTES + C::A_BYTES;
+                mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+                tma_load_2d(b_dst, &tmB, (int32_t)((kb_begin + i) * GB_K), (int32_t)n0, &full_bar[i]);
+            }
+            pdl_wait();
+            for (uint32_t i = 0; i < pre; i++)
+                tma_load_2d(smem + (size_t)i * C::STAGE_BYTES, &tmA, (int32_t)((kb_begin + i) * GB_K), (int32_t)m0, &full_bar[i]);
+            for (uint32_t i = pre; i < num_kb; i++) {
                 const uint32_t s = i % stages, ph = (i / stages) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); break; }
                 uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
@@ -258,6 +270,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t row = m0 + trow;
     bool got = true;
     if (warp >= 2) {
+        pdl_wait();  // the epilogue reads and writes C: never before the preceding kernels are done
         got = mbar_wait(&acc_bar, 0);
         if (!got && lane == 0) atomicExch(&fail_flag, 3u);
         tc_fence_after();
@@ -369,12 +382,16 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
     GemmPlan p{};
     p.kseg = 1;
     if (m > GB_M && invariant && allow_split) {
-        // same K partition as the skinny plan of this (n, k), done inside one CTA
+        // same K partition as the skinny plan of this (n, k)
         const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
         if (sk.ks > 1) {
             p.kseg = sk.ks;
             p.ks = 1;
+            // widest tile whose accumulators fit TMEM (kseg * bn <= 512 columns); narrower while
+            // the grid would leave most SMs idle (a prompt or two joining a decode batch)
             p.bn = 512 / sk.ks > 256 ? 256 : 512 / sk.ks;
+            const uint32_t mt = cdiv(m, GB_M);
+            while (p.bn > 32 && (uint64_t)mt * cdiv(n, p.bn) < 148) p.bn /= 2;
             uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
             if (st > G_MAX_STAGES) st = G_MAX_STAGES;
             if (p.bn <= 64 && st > 6) st = 6;

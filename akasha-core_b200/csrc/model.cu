@@ -2,6 +2,7 @@
 #include "model.h"
 
 #include <math.h>
+#include <limits.h>
 #include <string.h>
 
 using namespace ak;
@@ -179,7 +180,7 @@ Runner::~Runner() {
     if (!ctx_) return;
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
-    if (graph_exec_) cudaGraphExecDestroy(graph_exec_);
+    for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     if (ev_attn0_) cudaEventDestroy(ev_attn0_);
     if (ev_attn1_) cudaEventDestroy(ev_attn1_);
     for (void* p : k_pool_) cudaFree(p);
@@ -360,43 +361,82 @@ int Runner::run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len
     return AK_OK;
 }
 
-int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
+static uint32_t pow2_bucket(uint32_t v, uint32_t lo) {
+    uint32_t b = lo;
+    while (b < v) b *= 2;
+    return b;
+}
+
+// A step through a captured CUDA graph. Launch shapes are rounded up to a bucket
+// (prefill rows: 0 or a power of two >= 64, capped at the step budget; prefilled sequences: a
+// power of two), the padding rows / sequences are marked inactive in the descriptor, and one
+// graph per bucket is captured on first use. Row results do not depend on the bucket (every
+// kernel treats rows independently and the GEMM's K order is fixed per (n, k)).
+int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len) {
+    AK_REQUIRE(n_prefill_rows <= max_pf_tokens_ && n_pf_seqs <= max_seqs_, AK_ERR_INVALID_ARG, "runner: step exceeds its budget");
     AK_CUDA(cudaSetDevice(ctx_->device));
     cudaStream_t st = ctx_->stream;
-    const uint32_t H = w_->cfg.num_heads;
-    // The split count is baked into the captured launch; it is chosen once from the longest
-    // sequence the runner can hold.
-    (void)max_kv_len_hint;
-    if (!graph_exec_) {
-        // one eager pass first: sets kernel attributes and faults early outside capture
-        int rc = run(0, 0, 0, true, max_seq_len_);
+    uint32_t rows_b = 0, seqs_b = 0, len_b = 0;
+    if (n_prefill_rows) {
+        rows_b = pow2_bucket(n_prefill_rows, 64);
+        if (rows_b > max_pf_tokens_) rows_b = max_pf_tokens_;
+        seqs_b = pow2_bucket(n_pf_seqs, 1);
+        if (seqs_b > max_seqs_) seqs_b = max_seqs_;
+        len_b = rows_b < max_seq_len_ ? rows_b : max_seq_len_;
+        (void)max_pf_len;
+        // mark the padding inactive
+        RowInfo* rows = h_rows();
+        for (uint32_t r = max_seqs_ + n_prefill_rows; r < max_seqs_ + rows_b; r++) rows[r] = {INT32_MIN, -1, -1, 0};
+        int32_t* cu = h_pf_cu();
+        int32_t* pfs = h_pf_slot();
+        for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; }
+    }
+    const uint64_t key = ((uint64_t)rows_b << 32) | seqs_b;
+    const uint32_t T = max_seqs_ + rows_b;
+    const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
+    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
+    auto it = graphs_.find(key);
+    if (it == graphs_.end()) {
+        // one eager pass first (sets kernel attributes, surfaces faults outside capture); it IS this step
+        AK_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st));
+        int rc = launch_layers(T, rows_b, seqs_b, len_b, true, n_splits, false);
         if (rc) return rc;
+        AK_CUDA(cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st));
         AK_CUDA(cudaStreamSynchronize(st));
-        graph_splits_ = attn_decode_pick_splits(max_seqs_, H, max_seq_len_);
+        eager_steps++;
+        h2d_bytes += bytes;
+        d2h_bytes += (size_t)max_seqs_ * 4;
         cudaGraph_t graph = nullptr;
         AK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-        const size_t bytes = ((size_t)d_.rows + (size_t)max_seqs_ * 4) * 4;
         cudaError_t e = cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st);
         const unsigned long long l0 = g_launch_count;
-        rc = (e == cudaSuccess) ? launch_layers(max_seqs_, 0, 0, 0, true, graph_splits_, true) : AK_ERR_CUDA;
-        graph_kernels = g_launch_count - l0;
+        rc = (e == cudaSuccess) ? launch_layers(T, rows_b, seqs_b, len_b, true, n_splits, true) : AK_ERR_CUDA;
+        StepGraph g;
+        g.kernels = g_launch_count - l0;
+        g.h2d = bytes;
         g_launch_count = l0;  // recorded into the graph, not launched
         if (rc == AK_OK) e = cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st);
         cudaError_t e2 = cudaStreamEndCapture(st, &graph);
         if (rc) return rc;
         if (e != cudaSuccess) return cuda_fail(e, "capture memcpy", __FILE__, __LINE__);
         if (e2 != cudaSuccess) return cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
-        AK_CUDA(cudaGraphInstantiate(&graph_exec_, graph, 0));
+        AK_CUDA(cudaGraphInstantiate(&g.exec, graph, 0));
         cudaGraphDestroy(graph);
-        // The eager pass above already executed this step: do not run it twice.
+        graphs_[key] = g;
+        if (key == 0) graph_kernels = g.kernels;
         return AK_OK;
     }
-    AK_CUDA(cudaGraphLaunch(graph_exec_, st));
+    AK_CUDA(cudaGraphLaunch(it->second.exec, st));
     graph_launches++;
-    g_launch_count += graph_kernels;
-    h2d_bytes += ((size_t)d_.rows + (size_t)max_seqs_ * 4) * 4;
+    g_launch_count += it->second.kernels;
+    h2d_bytes += it->second.h2d;
     d2h_bytes += (size_t)max_seqs_ * 4;
     return AK_OK;
+}
+
+int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
+    (void)max_kv_len_hint;
+    return run_graph(0, 0, 0);
 }
 
 int Runner::sync() {

@@ -2,6 +2,7 @@
 // `ModelWeights::params()` order, and the ragged-batch runner that launches one kernel per
 // layer-op over all token rows of a step.
 #pragma once
+#include <map>
 #include <vector>
 
 #include "kernels.h"
@@ -75,6 +76,8 @@ class Runner {
     int run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t max_kv_len);
     // Decode-only step through a captured CUDA graph (captured on first use).
     int run_decode_graph(uint32_t max_kv_len_hint);
+    // Any step (decode rows + optional prefill rows) through a per-bucket captured graph.
+    int run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len);
     int sync();
     int read_logits(uint32_t slot, float* host_out);
     int gather_cache(uint32_t layer, const int32_t* h_table, uint32_t len, float* k_out, float* v_out);
@@ -121,8 +124,12 @@ class Runner {
     size_t attn_scratch_bytes_ = 0;
     float2* rope_table_ = nullptr;
     uint32_t rope_len_ = 0;
-    cudaGraphExec_t graph_exec_ = nullptr;
-    uint32_t graph_splits_ = 0;
+    struct StepGraph {
+        cudaGraphExec_t exec = nullptr;
+        uint64_t kernels = 0;
+        size_t h2d = 0;
+    };
+    std::map<uint64_t, StepGraph> graphs_;  // key = (prefill row bucket << 32) | prefill sequence bucket
     bool attn_timing_ = false;
     cudaEvent_t ev_attn0_ = nullptr, ev_attn1_ = nullptr;
     bool ev_valid_ = false;

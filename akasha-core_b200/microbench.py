@@ -139,7 +139,7 @@ def bench_engine(ak, torch, iters, small):
     w = ak.ModelWeights(ctx, cfg, ak.AK_BF16)
     w.init_synthetic(0, 0.02)
     eng = ak.Engine(ctx, w, max_seqs=64, max_seq_len=512, use_cuda_graph=True, attn_timing=True)
-    lens = ak.uniform_ints(64, 16, 448, seed=2)
+    lens = ak.uniform_ints(63 if "--mixed" in sys.argv else 64, 16, 448, seed=2)
     for i, l in enumerate(lens):
         eng.submit(ak.uniform_tokens(int(l), cfg.vocab_size, seed=100 + i), 512)
     warm = 4 if small else 40
@@ -151,10 +151,23 @@ def bench_engine(ak, torch, iters, small):
         eng.step()
     dt = (time.perf_counter() - t0) / iters
     st = eng.stats()
+    mixed = None
+    if "--mixed" in sys.argv:
+        # a steady-state admission: one more 232-token prompt joins 63 running sequences
+        mixed = []
+        for rep in range(3):
+            eng.submit(ak.uniform_tokens(232, cfg.vocab_size, seed=999 + rep), 232 + 3)
+            t1 = time.perf_counter()
+            eng.step()
+            mixed.append((time.perf_counter() - t1) * 1e3)
+            for _ in range(4):
+                eng.step()
     out = {"kernel": "engine decode step (162M, 64 seqs)", "ms_per_step": dt * 1e3, "tok/s": 64 / dt,
            "kernels_per_step": st["kernel_launches"] / max(1, st["steps"]),
            "attn_us_layer0": 1e3 * st["attn_ms_total"] / max(1, st["attn_launches_timed"]),
            "attn_GB/s": st["attn_bytes_total"] / max(1e-9, st["attn_ms_total"] * 1e-3) / 1e9}
+    if mixed:
+        out["mixed_step_ms"] = mixed   # first entry includes the bucket's graph capture
     eng.close(); w.close(); ctx.close()
     return out
 
