@@ -118,6 +118,9 @@ _PROTOS = {
     "ak_ctx_create": [C.c_int, C.POINTER(vp)],
     "ak_ctx_destroy": [vp],
     "ak_ctx_synchronize": [vp],
+    "ak_tp_unique_id": [vp],
+    "ak_ctx_tp_init": [vp, C.c_uint32, C.c_uint32, vp],
+    "ak_ctx_tp_shutdown": [vp],
     "ak_weights_create": [vp, C.POINTER(_ModelConfig), C.c_uint32, C.POINTER(vp)],
     "ak_weights_destroy": [vp],
     "ak_weights_set_param": [vp, C.c_uint32, f32p, C.c_uint64],
@@ -308,6 +311,19 @@ class Context:
 
     def synchronize(self):
         check(lib().ak_ctx_synchronize(self.h))
+
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """128-byte NCCL id made by tensor-parallel rank 0; hand it to the other ranks."""
+        buf = C.create_string_buffer(128)
+        check(lib().ak_tp_unique_id(buf))
+        return buf.raw
+
+    def tp_init(self, tp_size: int, tp_rank: int, unique_id: bytes):
+        """Join a tensor-parallel group; call before creating weights on this context."""
+        assert len(unique_id) == 128
+        check(lib().ak_ctx_tp_init(self.h, tp_size, tp_rank, C.create_string_buffer(unique_id, 128)))
+        self.tp_size, self.tp_rank = tp_size, tp_rank
 
     def check_device_status(self):
         check(lib().ak_check_device_status(self.stream))

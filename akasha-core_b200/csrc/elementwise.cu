@@ -560,6 +560,41 @@ __global__ void fill_normal_kernel(T* __restrict__ dst, size_t n, uint64_t seed,
         dst[i] = Cvt<T>::from_f(mean + std * z);
     }
 }
+template <typename T>
+__global__ void fill_normal_2d_kernel(T* __restrict__ dst, bool transposed, uint32_t lin, uint32_t lout, uint32_t gout,
+                                      uint32_t row_off, uint32_t col_mode, uint32_t col_off, uint32_t blk_l, uint32_t blk_g,
+                                      uint64_t seed, uint64_t stream_id, float mean, float std) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (size_t)gridDim.x * blockDim.x;
+    const size_t n = (size_t)lin * lout;
+    uint64_t base = splitmix64(seed ^ splitmix64(stream_id * 0x632BE59BD9B4E019ull + 1));
+    for (; i < n; i += stride) {
+        // i runs over the STORAGE order, so writes stay coalesced
+        uint32_t r, c;
+        if (transposed) { c = (uint32_t)(i / lin); r = (uint32_t)(i % lin); }
+        else { r = (uint32_t)(i / lout); c = (uint32_t)(i % lout); }
+        uint32_t gc = (col_mode == 3) ? (c / blk_l) * blk_g + col_off + c % blk_l : col_off + c;
+        uint64_t g = (uint64_t)(r + row_off) * gout + gc;
+        uint64_t rr = splitmix64(base + g);
+        float u1 = ((float)((rr >> 40) & 0xFFFFFF) + 1.0f) / 16777217.0f;
+        float u2 = (float)((rr >> 8) & 0xFFFFFF) / 16777216.0f;
+        float z = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+        dst[i] = Cvt<T>::from_f(mean + std * z);
+    }
+}
+int launch_fill_normal_2d(cudaStream_t st, void* dst, uint32_t dtype, bool transposed, uint32_t lin, uint32_t lout,
+                          uint32_t gout, uint32_t row_off, uint32_t col_mode, uint32_t col_off, uint32_t blk_l,
+                          uint32_t blk_g, uint64_t seed, uint64_t stream_id, float mean, float std) {
+    size_t n = (size_t)lin * lout;
+    if (!n) return AK_OK;
+    if (dtype == AK_F32)
+        fill_normal_2d_kernel<float><<<stride_blocks(n), 256, 0, st>>>((float*)dst, transposed, lin, lout, gout, row_off, col_mode, col_off, blk_l, blk_g, seed, stream_id, mean, std);
+    else
+        fill_normal_2d_kernel<bf16><<<stride_blocks(n), 256, 0, st>>>((bf16*)dst, transposed, lin, lout, gout, row_off, col_mode, col_off, blk_l, blk_g, seed, stream_id, mean, std);
+    AK_COUNT_LAUNCH();
+    AK_CHECK_LAUNCH();
+    return AK_OK;
+}
+
 int launch_fill_normal(cudaStream_t st, void* dst, uint32_t dtype, uint64_t n, uint64_t seed, uint64_t stream_id,
                        float mean, float std) {
     if (!n) return AK_OK;

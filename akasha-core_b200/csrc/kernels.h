@@ -35,6 +35,13 @@ int launch_transpose_to_bf16(cudaStream_t st, const float* w_kn, void* wt_nk, ui
 int launch_transpose_from_bf16(cudaStream_t st, const void* wt_nk, float* w_kn, uint32_t k, uint32_t n);
 int launch_fill_normal(cudaStream_t st, void* dst, uint32_t dtype, uint64_t n, uint64_t seed, uint64_t stream_id,
                        float mean, float std);
+// Matrix fill for (possibly sliced) weights: local element (i, c) of a [lin, lout] slice takes the
+// value of the FULL matrix element it corresponds to, so every tensor-parallel rank and the
+// single-GPU run hold the same model. col_mode 0: gc = col_off + c; 3: fused qkv blocks
+// (gc = (c / blk_l) * blk_g + col_off + c % blk_l). transposed: storage is [lout, lin].
+int launch_fill_normal_2d(cudaStream_t st, void* dst, uint32_t dtype, bool transposed, uint32_t lin, uint32_t lout,
+                          uint32_t gout, uint32_t row_off, uint32_t col_mode, uint32_t col_off, uint32_t blk_l,
+                          uint32_t blk_g, uint64_t seed, uint64_t stream_id, float mean, float std);
 // Gather a sequence's paged rows back into the reference's contiguous [len, heads*head_dim] f32.
 int launch_gather_paged(cudaStream_t st, const void* pool, uint32_t kv_dtype, const int32_t* block_table,
                         float* out, uint32_t len, uint32_t heads, uint32_t head_dim, uint32_t block_size);
@@ -69,6 +76,12 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
                              const ak_attn_decode_params& p);
 
 int attn_decode_status(unsigned int* out);  // device status word of the decode kernel
+
+}  // namespace ak
+struct ak_ctx;
+namespace ak {
+// ---- tp.cu: in-place sum over the tensor-parallel group (no-op when tp_size == 1)
+int tp_all_reduce_f32(ak_ctx* ctx, float* buf, size_t count);
 
 // ---- attn_prefill.cu ---------------------------------------------------------------------------
 // Causal varlen attention over newly prefilled sequences. q/out rows of sequence i are

@@ -26,9 +26,11 @@ int ak_ctx_create(int device, ak_ctx** out) {
     *out = c;
     return AK_OK;
 }
+int ak_ctx_tp_shutdown(ak_ctx* ctx);
 int ak_ctx_destroy(ak_ctx* ctx) {
     if (!ctx) return AK_OK;
     cudaSetDevice(ctx->device);
+    ak_ctx_tp_shutdown(ctx);
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return AK_OK;
@@ -55,27 +57,46 @@ int ak_weights_create(ak_ctx* ctx, const ak_model_config* cfg, uint32_t dtype, a
                    "ak_weights_create: bf16 mode needs dim, ffn_hidden and head_dim to be multiples of 8");
     else
         AK_REQUIRE(hd % 4 == 0, AK_ERR_UNSUPPORTED, "ak_weights_create: head_dim must be a multiple of 4");
+    const uint32_t tp = ctx->tp_size;
+    AK_REQUIRE(cfg->num_heads % tp == 0 && cfg->ffn_hidden % tp == 0, AK_ERR_INVALID_ARG,
+               "ak_weights_create: heads and ffn_hidden must be divisible by the tensor-parallel size %u", tp);
+    if (dtype == AK_BF16) AK_REQUIRE((cfg->ffn_hidden / tp) % 8 == 0, AK_ERR_UNSUPPORTED, "ak_weights_create: ffn_hidden / tp must be a multiple of 8");
     AK_CUDA(cudaSetDevice(ctx->device));
     ak_weights* w = new ak_weights();
     w->ctx = ctx;
     w->cfg = *cfg;
     w->dtype = dtype;
+    w->tp_size = tp;
+    w->tp_rank = ctx->tp_rank;
     const uint64_t V = cfg->vocab_size, D = cfg->dim, F = cfg->ffn_hidden;
+    const uint32_t Dl = (uint32_t)D / tp, Fl = (uint32_t)F / tp;
     w->blocks.resize(cfg->num_layers);
-    auto add = [&](void** p, uint64_t len, uint32_t kind, uint32_t in, uint32_t o) { w->params.push_back({p, len, kind, in, o}); };
-    add(&w->embedding, V * D, 1, (uint32_t)V, (uint32_t)D);
+    // split: 0 whole, 1 rows, 2 columns, 3 fused-qkv columns (only when tp > 1)
+    auto add = [&](void** p, uint64_t len, uint32_t kind, uint32_t in, uint32_t o, uint32_t split) {
+        ak_weights::ParamRef pr{};
+        pr.ptr = p; pr.len = len; pr.kind = kind; pr.in = in; pr.out = o;
+        pr.split = tp > 1 ? split : 0;
+        pr.lin = in; pr.lout = o;
+        if (pr.split == 1) pr.lin = in / tp;
+        if (pr.split == 2) pr.lout = o / tp;
+        if (pr.split == 3) pr.lout = 3 * Dl;
+        pr.llen = kind == 0 ? len : (uint64_t)pr.lin * pr.lout;
+        w->params.push_back(pr);
+    };
+    (void)Fl;
+    add(&w->embedding, V * D, 1, (uint32_t)V, (uint32_t)D, 0);
     for (auto& b : w->blocks) {
-        add((void**)&b.norm_1, D, 0, 0, 0);
-        add(&b.qkv, D * 3 * D, 2, (uint32_t)D, (uint32_t)(3 * D));
-        add(&b.out, D * D, 2, (uint32_t)D, (uint32_t)D);
-        add((void**)&b.norm_2, D, 0, 0, 0);
-        add(&b.up, D * F, 2, (uint32_t)D, (uint32_t)F);
-        add(&b.down, F * D, 2, (uint32_t)F, (uint32_t)D);
+        add((void**)&b.norm_1, D, 0, 0, 0, 0);
+        add(&b.qkv, D * 3 * D, 2, (uint32_t)D, (uint32_t)(3 * D), 3);  // heads split: columns of q, k and v
+        add(&b.out, D * D, 2, (uint32_t)D, (uint32_t)D, 1);            // rows follow the local heads
+        add((void**)&b.norm_2, D, 0, 0, 0, 0);
+        add(&b.up, D * F, 2, (uint32_t)D, (uint32_t)F, 2);
+        add(&b.down, F * D, 2, (uint32_t)F, (uint32_t)D, 1);
     }
-    add((void**)&w->final_norm, D, 0, 0, 0);
-    add(&w->lm_head, D * V, 2, (uint32_t)D, (uint32_t)V);
+    add((void**)&w->final_norm, D, 0, 0, 0, 0);
+    add(&w->lm_head, D * V, 2, (uint32_t)D, (uint32_t)V, 0);
     for (auto& pr : w->params) {
-        size_t bytes = pr.len * (pr.kind == 0 ? 4 : welem(dtype));
+        size_t bytes = pr.llen * (pr.kind == 0 ? 4 : welem(dtype));
         cudaError_t e = cudaMalloc(pr.ptr, bytes);
         if (e != cudaSuccess) {
             ak_weights_destroy(w);
@@ -121,14 +142,28 @@ int ak_weights_set_param(ak_weights* w, uint32_t index, const float* host, uint6
                (unsigned long long)pr.len, (unsigned long long)n_elems);
     AK_CUDA(cudaSetDevice(w->ctx->device));
     cudaStream_t st = w->ctx->stream;
+    // tensor-parallel slice of the full host tensor (the caller always passes the whole tensor)
+    std::vector<float> slice;
+    const float* src = host;
+    if (pr.split == 1) {
+        src = host + (size_t)w->tp_rank * pr.lin * pr.out;  // contiguous block of rows
+    } else if (pr.split == 2 || pr.split == 3) {
+        slice.resize(pr.llen);
+        const uint32_t nblk = pr.split == 3 ? 3 : 1;
+        const uint32_t bl = pr.lout / nblk, bg = pr.out / nblk;  // local / global block width
+        for (uint32_t i = 0; i < pr.lin; i++)
+            for (uint32_t b = 0; b < nblk; b++)
+                memcpy(&slice[(size_t)i * pr.lout + (size_t)b * bl], host + (size_t)i * pr.out + (size_t)b * bg + (size_t)w->tp_rank * bl, (size_t)bl * 4);
+        src = slice.data();
+    }
     if (w->dtype == AK_F32 || pr.kind == 0) {
-        AK_CUDA(cudaMemcpyAsync(*pr.ptr, host, pr.len * 4, cudaMemcpyHostToDevice, st));
+        AK_CUDA(cudaMemcpyAsync(*pr.ptr, src, pr.llen * 4, cudaMemcpyHostToDevice, st));
     } else {
-        int rc = ensure_staging(w, pr.len);
+        int rc = ensure_staging(w, pr.llen);
         if (rc) return rc;
-        AK_CUDA(cudaMemcpyAsync(w->staging, host, pr.len * 4, cudaMemcpyHostToDevice, st));
-        rc = (pr.kind == 1) ? launch_f32_to_bf16(st, w->staging, *pr.ptr, pr.len)
-                            : launch_transpose_to_bf16(st, w->staging, *pr.ptr, pr.in, pr.out);
+        AK_CUDA(cudaMemcpyAsync(w->staging, src, pr.llen * 4, cudaMemcpyHostToDevice, st));
+        rc = (pr.kind == 1) ? launch_f32_to_bf16(st, w->staging, *pr.ptr, pr.llen)
+                            : launch_transpose_to_bf16(st, w->staging, *pr.ptr, pr.lin, pr.lout);
         if (rc) return rc;
     }
     AK_CUDA(cudaStreamSynchronize(st));
@@ -140,6 +175,7 @@ int ak_weights_get_param(ak_weights* w, uint32_t index, float* host, uint64_t n_
     AK_REQUIRE(index < w->params.size(), AK_ERR_INVALID_ARG, "ak_weights_get_param: index %u out of range", index);
     auto& pr = w->params[index];
     AK_REQUIRE(n_elems == pr.len, AK_ERR_INVALID_ARG, "ak_weights_get_param: tensor %u holds %llu elements", index, (unsigned long long)pr.len);
+    AK_REQUIRE(pr.split == 0, AK_ERR_UNSUPPORTED, "ak_weights_get_param: tensor %u is sliced across tensor-parallel ranks", index);
     AK_CUDA(cudaSetDevice(w->ctx->device));
     cudaStream_t st = w->ctx->stream;
     if (w->dtype == AK_F32 || pr.kind == 0) {
@@ -161,8 +197,17 @@ int ak_weights_init_synthetic(ak_weights* w, uint64_t seed, float std) {
     AK_CUDA(cudaSetDevice(w->ctx->device));
     for (size_t i = 0; i < w->params.size(); i++) {
         auto& pr = w->params[i];
-        int rc = launch_fill_normal(w->ctx->stream, *pr.ptr, pr.kind == 0 ? (uint32_t)AK_F32 : w->dtype, pr.len, seed, i,
+        int rc;
+        if (pr.kind == 2) {
+            const uint32_t nblk = pr.split == 3 ? 3 : 1;
+            const uint32_t bl = pr.lout / nblk, bg = pr.out / nblk;
+            rc = launch_fill_normal_2d(w->ctx->stream, *pr.ptr, w->dtype, w->dtype == AK_BF16, pr.lin, pr.lout, pr.out,
+                                       pr.split == 1 ? w->tp_rank * pr.lin : 0, pr.split == 3 ? 3 : 0,
+                                       (pr.split == 2 || pr.split == 3) ? w->tp_rank * bl : 0, bl, bg, seed, i, 0.0f, std);
+        } else {
+            rc = launch_fill_normal(w->ctx->stream, *pr.ptr, pr.kind == 0 ? (uint32_t)AK_F32 : w->dtype, pr.len, seed, i,
                                     pr.kind == 0 ? 1.0f : 0.0f, std);
+        }
         if (rc) return rc;
     }
     AK_CUDA(cudaStreamSynchronize(w->ctx->stream));
@@ -186,7 +231,7 @@ Runner::~Runner() {
     for (void* p : k_pool_) cudaFree(p);
     for (void* p : v_pool_) cudaFree(p);
     cudaFree(hidden_); cudaFree(xn_); cudaFree(qkv_); cudaFree(qbuf_); cudaFree(attn_); cudaFree(up_);
-    cudaFree(amax_val_); cudaFree(amax_idx_);
+    cudaFree(amax_val_); cudaFree(amax_idx_); cudaFree(tp_tmp_);
     cudaFree(xf_); cudaFree(logits_); cudaFree(attn_scratch_); cudaFree(rope_table_);
     cudaFree(d_desc_); cudaFree(d_sampled_);
     if (h_desc_) cudaFreeHost(h_desc_);
@@ -206,6 +251,11 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     max_pf_tokens_ = max_prefill_tokens;
     max_rows_ = max_seqs + max_prefill_tokens;
     const size_t act = welem(w->dtype);
+    AK_REQUIRE(w->tp_size == ctx->tp_size && w->tp_rank == ctx->tp_rank, AK_ERR_INVALID_ARG, "runner: weights and context disagree on the tensor-parallel layout");
+    tp_ = w->tp_size;
+    heads_l_ = H / tp_;
+    dq_ = heads_l_ * hd;
+    ffn_l_ = F / tp_;
 
     d_.kv_lens = 0;
     d_.out_rows = d_.kv_lens + max_seqs;
@@ -223,7 +273,7 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaMalloc((void**)&d_sampled_, (size_t)max_seqs * 4));
     AK_CUDA(cudaMemset(d_sampled_, 0, (size_t)max_seqs * 4));
 
-    const size_t pool_bytes = (size_t)n_blocks_ * H * 16 * hd * act;
+    const size_t pool_bytes = (size_t)n_blocks_ * heads_l_ * 16 * hd * act;  // each rank caches its own heads
     k_pool_.assign(c.num_layers, nullptr);
     v_pool_.assign(c.num_layers, nullptr);
     for (uint32_t l = 0; l < c.num_layers; l++) {
@@ -235,10 +285,14 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     const size_t R = max_rows_;
     AK_CUDA(cudaMalloc((void**)&hidden_, R * D * 4));
     AK_CUDA(cudaMalloc(&xn_, R * D * act));
-    AK_CUDA(cudaMalloc((void**)&qkv_, R * 3 * D * 4));
-    AK_CUDA(cudaMalloc(&qbuf_, R * D * act));
-    AK_CUDA(cudaMalloc(&attn_, R * D * act));
-    AK_CUDA(cudaMalloc(&up_, R * F * act));
+    AK_CUDA(cudaMalloc((void**)&qkv_, R * 3 * dq_ * 4));
+    AK_CUDA(cudaMalloc(&qbuf_, R * dq_ * act));
+    AK_CUDA(cudaMalloc(&attn_, R * dq_ * act));
+    AK_CUDA(cudaMalloc(&up_, R * ffn_l_ * act));
+    if (tp_ > 1) {
+        AK_CUDA(cudaMalloc((void**)&tp_tmp_, R * D * 4));
+        AK_CUDA(cudaMemsetAsync(tp_tmp_, 0, R * D * 4, ctx->stream));
+    }
     AK_CUDA(cudaMalloc(&xf_, (size_t)max_seqs * D * act));
     logits_ld_ = (w->dtype == AK_BF16) ? (V + 3) / 4 * 4 : V;
     AK_CUDA(cudaMalloc((void**)&logits_, (size_t)max_seqs * logits_ld_ * 4));
@@ -249,12 +303,12 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     }
     AK_CUDA(cudaMemsetAsync(hidden_, 0, R * D * 4, ctx->stream));
     AK_CUDA(cudaMemsetAsync(xn_, 0, R * D * act, ctx->stream));
-    AK_CUDA(cudaMemsetAsync(qkv_, 0, R * 3 * D * 4, ctx->stream));
-    AK_CUDA(cudaMemsetAsync(qbuf_, 0, R * D * act, ctx->stream));
-    AK_CUDA(cudaMemsetAsync(attn_, 0, R * D * act, ctx->stream));
-    AK_CUDA(cudaMemsetAsync(up_, 0, R * F * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(qkv_, 0, R * 3 * dq_ * 4, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(qbuf_, 0, R * dq_ * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(attn_, 0, R * dq_ * act, ctx->stream));
+    AK_CUDA(cudaMemsetAsync(up_, 0, R * ffn_l_ * act, ctx->stream));
     AK_CUDA(cudaMemsetAsync(logits_, 0, (size_t)max_seqs * logits_ld_ * 4, ctx->stream));
-    attn_scratch_bytes_ = attn_decode_scratch_bytes(max_seqs, H, hd, 32);
+    attn_scratch_bytes_ = attn_decode_scratch_bytes(max_seqs, heads_l_, hd, 32);
     AK_CUDA(cudaMalloc((void**)&attn_scratch_, attn_scratch_bytes_));
 
     // RoPE factors from the host libm, exactly as the reference's CPU kernel forms them
@@ -290,17 +344,25 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                           uint32_t n_splits, bool capturing) {
     cudaStream_t st = ctx_->stream;
     const ak_model_config& c = w_->cfg;
-    const uint32_t D = c.dim, F = c.ffn_hidden, V = c.vocab_size, H = c.num_heads, hd = D / H;
+    // With tensor parallelism (tp_ > 1) this rank holds heads_l_ heads (dq_ = heads_l_*hd columns of
+    // q, k and v) and ffn_l_ ffn columns; the row-split out-proj / ffn-down products are partial
+    // sums that go to tp_tmp_, are all-reduced, and are folded into the residual stream by the
+    // rmsnorm that follows (h = hidden + sum, written back).
+    const uint32_t D = c.dim, V = c.vocab_size, hd = D / c.num_heads, H = heads_l_, Dq = dq_, F = ffn_l_;
     const uint32_t dt = w_->dtype;
     const float scale = 1.0f / sqrtf((float)hd);
     const int32_t* rows = d_desc_ + d_.rows;
+    const bool tp = tp_ > 1;
+    bool pending = false;  // tp_tmp_ holds a reduced projection not yet added to hidden_
     int rc;
 #define RC(x) do { rc = (x); if (rc) return rc; } while (0)
     RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const auto& b = w_->blocks[l];
-        RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
-        RC(gemm(xn_, b.qkv, qkv_, T, 3 * D, D, 0));
+        if (pending) RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_1, xn_, nullptr, T, D, c.norm_eps, 0, dt));
+        else RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
+        pending = false;
+        RC(gemm(xn_, b.qkv, qkv_, T, 3 * Dq, D, 0));
         RC(launch_rope_kv_append(st, qkv_, rows + 1, rows + 2, 4, qbuf_, k_pool_[l], v_pool_[l], rope_table_, rope_len_, T, H, hd, 16, dt));
         if (any_decode) {
             ak_attn_decode_params p{};
@@ -322,11 +384,25 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
             RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
                                          d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt));
         }
-        RC(gemm(attn_, b.out, hidden_, T, D, D, 1));
-        RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
+        if (tp) {
+            RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));
+            RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
+            RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_2, xn_, nullptr, T, D, c.norm_eps, 0, dt));
+        } else {
+            RC(gemm(attn_, b.out, hidden_, T, D, Dq, 1));
+            RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
+        }
         RC(gemm(xn_, b.up, up_, T, F, D, 2));
-        RC(gemm(up_, b.down, hidden_, T, D, F, 1));
+        if (tp) {
+            RC(gemm(up_, b.down, tp_tmp_, T, D, F, 0));
+            RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
+            pending = true;
+        } else {
+            RC(gemm(up_, b.down, hidden_, T, D, F, 1));
+        }
     }
+    if (pending)  // fold the last ffn-down sum into the residual stream (the normalised output is not used)
+        RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, w_->final_norm, xn_, nullptr, T, D, c.norm_eps, 0, dt));
     RC(launch_rmsnorm(st, hidden_, w_->final_norm, xf_, dt, d_desc_ + d_.out_rows, max_seqs_, D, c.norm_eps));
     if (dt == AK_BF16) {
         // greedy argmax fused into the lm_head epilogue: logits are written only when someone reads them

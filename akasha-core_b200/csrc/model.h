@@ -10,6 +10,9 @@
 struct ak_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
+    // tensor parallelism (1 = off): this context is rank tp_rank of tp_size, tp_comm = ncclComm_t
+    uint32_t tp_size = 1, tp_rank = 0;
+    void* tp_comm = nullptr;
 };
 
 struct ak_weights {
@@ -38,8 +41,14 @@ struct ak_weights {
         void** ptr;
         uint64_t len;
         uint32_t kind;  // 0 = norm gain (f32), 1 = embedding table, 2 = matrix [in,out]
-        uint32_t in, out;
+        uint32_t in, out;    // full (reference) shape
+        // tensor-parallel slice held by this rank: 0 = whole tensor, 1 = rows (in) split,
+        // 2 = columns (out) split, 3 = the fused qkv matrix: each of its q|k|v column blocks split
+        uint32_t split = 0;
+        uint32_t lin = 0, lout = 0;  // local shape
+        uint64_t llen = 0;           // local element count
     };
+    uint32_t tp_size = 1, tp_rank = 0;
     std::vector<ParamRef> params;  // params() order
 };
 
@@ -120,6 +129,8 @@ class Runner {
     float* amax_val_ = nullptr;       // per-tile row maxima of the lm_head (bf16 mode)
     uint32_t* amax_idx_ = nullptr;
     uint32_t amax_tiles_ = 0;
+    float* tp_tmp_ = nullptr;         // [rows, dim] f32 partial of the row-split projections (tp > 1)
+    uint32_t tp_ = 1, heads_l_ = 0, dq_ = 0, ffn_l_ = 0;  // local heads, local q width, local ffn width
     float* attn_scratch_ = nullptr;
     size_t attn_scratch_bytes_ = 0;
     float2* rope_table_ = nullptr;

@@ -232,6 +232,17 @@ AK_API int ak_ctx_destroy(ak_ctx* ctx);
 AK_API int ak_ctx_synchronize(ak_ctx* ctx);
 AK_API void* ak_ctx_stream(ak_ctx* ctx);
 
+/* Tensor parallelism (new: the reference runs on one device, src/main.rs:366). One process per
+ * GPU; rank 0 makes an id with ak_tp_unique_id (128 bytes, ncclUniqueId), the host passes it to the
+ * other ranks by its own means, and every rank calls ak_ctx_tp_init BEFORE creating weights.
+ * Weights created on such a context hold this rank's slice (heads split over the fused qkv
+ * columns and the out-proj rows, ffn columns / ffn-down rows); ak_weights_set_param still takes
+ * the FULL tensor and keeps the slice. Sessions and engines then all-reduce (NCCL, sum, f32) the
+ * partial out-proj and ffn-down products. All ranks must issue the same calls in the same order. */
+AK_API int ak_tp_unique_id(void* out128);
+AK_API int ak_ctx_tp_init(ak_ctx* ctx, uint32_t tp_size, uint32_t tp_rank, const void* unique_id128);
+AK_API int ak_ctx_tp_shutdown(ak_ctx* ctx);
+
 /* ModelWeights::zeros (src/nn/weights.rs:124-156): allocate all tensors, zero-filled. */
 AK_API int ak_weights_create(ak_ctx* ctx, const ak_model_config* cfg, uint32_t dtype, ak_weights** out);
 AK_API int ak_weights_destroy(ak_weights* w);
