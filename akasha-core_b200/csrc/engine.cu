@@ -169,7 +169,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
             any_decode = true;
             n_dec++;
             if (pos + 1 > max_kv) max_kv = pos + 1;
-            attn_bytes += (uint64_t)(pos + 1) * mc.dim * 2 * esz + (uint64_t)mc.dim * 2 * esz + (uint64_t)((pos + 16) / 16) * 4;
+            const uint64_t qd = r.local_qdim();  // this rank's share of the heads
+            attn_bytes += (uint64_t)(pos + 1) * qd * 2 * esz + qd * 2 * esz + (uint64_t)((pos + 16) / 16) * 4;
         } else {
             rows[i] = {INT_MIN, -1, -1, (int32_t)i};
             kv[i] = 0;

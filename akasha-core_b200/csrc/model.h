@@ -96,6 +96,7 @@ class Runner {
     uint32_t n_blocks() const { return n_blocks_; }
     uint32_t max_prefill_tokens() const { return max_pf_tokens_; }
     uint32_t dtype() const { return w_->dtype; }
+    uint32_t local_qdim() const { return dq_; }  // heads held by this rank x head_dim
     void enable_attn_timing(bool on) { attn_timing_ = on; }
     void set_keep_logits(bool on) { keep_logits_ = on; }
     float last_attn_ms();
