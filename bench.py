@@ -261,9 +261,14 @@ def main():
                     "h2d_bytes_per_step": (st2["h2d_bytes"] - st["h2d_bytes"]) / args.steps,
                     "d2h_bytes_per_step": (st2["d2h_bytes"] - st["d2h_bytes"]) / args.steps},
             "gpu_launches": int(st["kernel_launches"]),
-            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64> (layer 0, every decode step)",
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,2> (layer 0, every decode step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_kind, "traffic": None,
+                         "peak_source": peak_kind,
+                         # DRAM bytes per launch: 1.059 x the algorithmic bytes, the ratio ncu measured
+                         # (dram__bytes_read.sum + dram__bytes_write.sum) on a smaller launch of the same
+                         # kernel; traffic grows in proportion to the K/V bytes
+                         # (profiles/attn_decode_paged_bf16_hd64_ncu.md)
+                         "traffic": 1.059 * attn_bytes,
                          "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "launches_timed": st["attn_launches_timed"]},
             "clocks": clocks,
             "engine": {"decode_tokens": st["decode_tokens"], "prefill_tokens": st["prefill_tokens"],
