@@ -22,6 +22,8 @@
 namespace ak {
 
 __device__ unsigned int g_attn_decode_status = 0;
+// Set by the runner around its own launches (host side, per thread): see `early` in the kernel.
+thread_local bool g_attn_early = false;
 
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_BS = 16;  // positions per KV block
@@ -63,8 +65,12 @@ __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const T* __restrict__ q, const int32_t* __restrict__ block_tables,
                          const int32_t* __restrict__ kv_lens, T* __restrict__ out, float* __restrict__ scratch,
-                         uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits) {
-    pdl_wait();
+                         uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits, uint32_t early) {
+    // `early` = the caller guarantees that the kernel launched just before this one wrote nothing of
+    // the cache except each sequence's newest position (the engine's append kernel). Then:
+    // Programmatic dependent launch: the descriptor arrays (lengths, block tables) and every KV
+    // block except the one holding the newest position were written before the preceding kernel
+    // started, so they are fetched BEFORE waiting for it; q and the newest block come after.
     pdl_trigger();
     using C = DecCfg<T, HD, ST>;
     extern __shared__ uint8_t smem_raw[];
@@ -93,20 +99,7 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
     __syncwarp();
 
-    // q slice of this lane: position pair-half hh = lane & 1 owns chunks [4hh, 4hh+4) of every group
     const uint32_t p = lane >> 1, hh = lane & 1;
-    float qreg[C::QREGS];
-    {
-        const T* qrow = q + (size_t)row * dim + (size_t)h * HD;
-#pragma unroll
-        for (int g = 0; g < C::GROUPS; g++)
-#pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint4 raw = *reinterpret_cast<const uint4*>(qrow + g * C::EPG + (4 * hh + c) * C::EPC);
-                unpack16<T>(raw, &qreg[(g * 4 + c) * C::EPC]);
-            }
-    }
-
     const int32_t* table = block_tables + (size_t)row * max_blocks;
     // blocks of this warp: b_begin + warp, + DEC_WARPS, ...
     const uint32_t first = b_begin + warp;
@@ -126,9 +119,31 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
     };
 
+    // first ring of loads; the block that holds the newest position (written by the preceding
+    // kernel) is held back until that kernel is known to be complete
+    const uint32_t pre = nmine < (uint32_t)C::STAGES ? nmine : (uint32_t)C::STAGES;
+    uint32_t deferred = 0xffffffffu;
+    if (!early) pdl_wait();
     if (lane == 0) {
-        uint32_t pre = nmine < (uint32_t)C::STAGES ? nmine : (uint32_t)C::STAGES;
-        for (uint32_t i = 0; i < pre; i++) issue(i);
+        for (uint32_t i = 0; i < pre; i++) {
+            if (early && first + i * DEC_WARPS + 1 == nblk) deferred = i;
+            else issue(i);
+        }
+    }
+    pdl_wait();
+    if (lane == 0 && deferred != 0xffffffffu) issue(deferred);
+
+    // q slice of this lane: position pair-half hh = lane & 1 owns chunks [4hh, 4hh+4) of every group
+    float qreg[C::QREGS];
+    {
+        const T* qrow = q + (size_t)row * dim + (size_t)h * HD;
+#pragma unroll
+        for (int g = 0; g < C::GROUPS; g++)
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+                uint4 raw = *reinterpret_cast<const uint4*>(qrow + g * C::EPG + (4 * hh + c) * C::EPC);
+                unpack16<T>(raw, &qreg[(g * 4 + c) * C::EPC]);
+            }
     }
 
     float m_run = -INFINITY, l_run = 0.0f;
@@ -382,7 +397,7 @@ static int launch_fast_st(cudaStream_t st, const void* q, const void* k_pool, co
     }
     dim3 grid(p.heads, p.rows, n_splits);
     AK_TRY(launch_k(attn_decode_paged_kernel<T, HD, ST>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, 
-        tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits));
+        tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits, (uint32_t)(g_attn_early ? 1 : 0)));
     if (n_splits > 1) {
         dim3 g2(p.heads, p.rows);
         AK_TRY(launch_k(attn_decode_combine_kernel<T, HD>, dim3(g2), dim3(32), 0, st, NO_CLUSTER, (const float*)scratch, (T*)out, p.heads, n_splits));

@@ -230,6 +230,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     if (graph) e->stats.graph_launches++; else e->stats.eager_steps++;
     e->stats.kernel_launches += (g_launch_count - launches0);
     e->stats.h2d_bytes = r.h2d_bytes;
+    e->stats.launch_host_ms_total = r.launch_host_ms;
+    if (e->cfg.attn_timing) e->stats.step_gpu_ms_total += r.last_step_gpu_ms();
     e->stats.d2h_bytes = r.d2h_bytes;
     if (e->cfg.attn_timing && any_decode) {
         float ms = r.last_attn_ms();

@@ -85,10 +85,17 @@ constexpr int G_MAX_STAGES = 8;
 // Cluster-wide barrier for all threads of all CTAs of the cluster. The .aligned forms need every
 // thread of a warp to execute them together, and the producer / MMA lanes run ahead of their
 // warps, so each warp is re-converged first.
-__device__ __forceinline__ void cluster_sync_all() {
+__device__ __forceinline__ void cluster_arrive_all() {
     __syncwarp();
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_all() {
+    __syncwarp();
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    cluster_arrive_all();
+    cluster_wait_all();
 }
 
 template <int BN> struct GemmCfg {
@@ -203,8 +210,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tmem_relinquish();
     }
     tc_fence_before();
-    if (ks > 1) cluster_sync_all();  // peers are running before anyone writes into their shared memory
-    else __syncthreads();
+    // "Every CTA of the cluster is running" must hold before anyone writes into a peer's shared
+    // memory. Arrive now, wait only right before the exchange: the barrier latency hides behind
+    // the main loop.
+    __syncthreads();
+    if (ks > 1) cluster_arrive_all();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sm;
     // Everything above touched only this CTA's shared memory and TMEM. Let the next kernel's blocks
@@ -316,6 +326,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     } else {
         // ---- scatter: columns [d*SL, (d+1)*SL) of my partial go to CTA d's exchange buffer slot `rank`
         const uint32_t SL = (uint32_t)BN / ks;  // multiple of 4 by construction of the launch
+        cluster_wait_all();  // phase 1: all peers are up (arrived at kernel start)
         if (warp >= 2 && got) {  // warp-uniform: tcgen05.ld is a warp-wide (.aligned) instruction
 #pragma unroll 1
             for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 16) {
@@ -432,7 +443,8 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
     for (int bi = 0; bi < 3; bi++)
         for (int ki = 0; ki < 4; ki++) {
             const uint32_t bn = bns[bi], ks = kss[ki];
-            if (ks > 1 && (!allow_split || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
+            // a cluster exchange costs more than it saves on short K chains: split only K > 1024
+            if (ks > 1 && (!allow_split || num_kb <= 16 || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
             const uint32_t per = cdiv(num_kb, ks);
             if (ks > 1 && (ks - 1) * per >= num_kb) continue;  // every CTA of the cluster gets work
             const uint32_t ctas = cdiv(n, bn) * ks;

@@ -76,6 +76,7 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
                              const ak_attn_decode_params& p);
 
 int attn_decode_status(unsigned int* out);  // device status word of the decode kernel
+extern thread_local bool g_attn_early;      // true while the runner launches (cache untouched but for the newest positions)
 
 }  // namespace ak
 struct ak_ctx;

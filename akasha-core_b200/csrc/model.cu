@@ -5,6 +5,10 @@
 #include <limits.h>
 #include <string.h>
 
+#include <stdlib.h>
+
+#include <chrono>
+
 using namespace ak;
 
 // ======================================================================== context
@@ -228,6 +232,8 @@ Runner::~Runner() {
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     if (ev_attn0_) cudaEventDestroy(ev_attn0_);
     if (ev_attn1_) cudaEventDestroy(ev_attn1_);
+    if (ev_g0_) cudaEventDestroy(ev_g0_);
+    if (ev_g1_) cudaEventDestroy(ev_g1_);
     for (void* p : k_pool_) cudaFree(p);
     for (void* p : v_pool_) cudaFree(p);
     cudaFree(hidden_); cudaFree(xn_); cudaFree(qkv_); cudaFree(qbuf_); cudaFree(attn_); cudaFree(up_);
@@ -325,6 +331,8 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaMemcpyAsync(rope_table_, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, ctx->stream));
     AK_CUDA(cudaEventCreate(&ev_attn0_));
     AK_CUDA(cudaEventCreate(&ev_attn1_));
+    AK_CUDA(cudaEventCreate(&ev_g0_));
+    AK_CUDA(cudaEventCreate(&ev_g1_));
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -355,7 +363,9 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
     const bool tp = tp_ > 1;
     bool pending = false;  // tp_tmp_ holds a reduced projection not yet added to hidden_
     int rc;
-#define RC(x) do { rc = (x); if (rc) return rc; } while (0)
+#define RC(x) do { rc = (x); if (rc) return rc; trace_mark(#x); } while (0)
+    gtrace_capture_ = capturing && T == max_seqs_;
+    trace_mark("begin");
     RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const auto& b = w_->blocks[l];
@@ -373,7 +383,10 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                 if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, st, cudaEventRecordExternal));
                 else AK_CUDA(cudaEventRecord(ev_attn0_, st));
             }
-            RC(launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p));
+            g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
+            rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
+            g_attn_early = false;
+            if (rc) return rc;
             if (timed) {
                 if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, st, cudaEventRecordExternal));
                 else AK_CUDA(cudaEventRecord(ev_attn1_, st));
@@ -502,7 +515,12 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
         if (key == 0) graph_kernels = g.kernels;
         return AK_OK;
     }
+    if (attn_timing_) AK_CUDA(cudaEventRecord(ev_g0_, st));
+    const auto h0 = std::chrono::steady_clock::now();
     AK_CUDA(cudaGraphLaunch(it->second.exec, st));
+    launch_host_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - h0).count();
+    if (attn_timing_) { AK_CUDA(cudaEventRecord(ev_g1_, st)); ev_g_valid_ = true; }
+    gtrace_ran_ = (key == 0);
     graph_launches++;
     g_launch_count += it->second.kernels;
     h2d_bytes += it->second.h2d;
@@ -515,9 +533,68 @@ int Runner::run_decode_graph(uint32_t max_kv_len_hint) {
     return run_graph(0, 0, 0);
 }
 
+void Runner::trace_mark(const char* label) {
+    static int on = -1;
+    if (on < 0) { const char* e = getenv("AK_TRACE"); on = (e && e[0] == '1') ? 1 : 0; }
+    if (!on) return;
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(ctx_->stream, &cs);
+    if (cs == cudaStreamCaptureStatusActive) {
+        if (!gtrace_capture_) return;
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        gtrace_ev_.push_back(ev);
+        gtrace_lbl_.push_back(label);
+        cudaEventRecordWithFlags(ev, ctx_->stream, cudaEventRecordExternal);
+        return;
+    }
+    if (trace_n_ == trace_ev_.size()) {
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        trace_ev_.push_back(ev);
+        trace_lbl_.push_back(label);
+    }
+    trace_lbl_[trace_n_] = label;
+    cudaEventRecord(trace_ev_[trace_n_++], ctx_->stream);
+}
+
+void Runner::trace_dump() {
+    if (gtrace_ran_ && gtrace_ev_.size() >= 2) {
+        gtrace_ran_ = false;
+        cudaStreamSynchronize(ctx_->stream);
+        fprintf(stderr, "[ak gtrace] %zu launches\n", gtrace_ev_.size() - 1);
+        for (size_t i = 1; i < gtrace_ev_.size(); i++) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, gtrace_ev_[i - 1], gtrace_ev_[i]) != cudaSuccess) { cudaGetLastError(); continue; }
+            fprintf(stderr, "[ak gtrace] %8.2f us  %.60s\n", ms * 1e3f, gtrace_lbl_[i]);
+        }
+    }
+    if (trace_n_ < 2) { trace_n_ = 0; return; }
+    cudaStreamSynchronize(ctx_->stream);
+    fprintf(stderr, "[ak trace] %zu launches\n", trace_n_ - 1);
+    for (size_t i = 1; i < trace_n_; i++) {
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, trace_ev_[i - 1], trace_ev_[i]);
+        fprintf(stderr, "[ak trace] %8.2f us  %.60s\n", ms * 1e3f, trace_lbl_[i]);
+    }
+    trace_n_ = 0;
+}
+
 int Runner::sync() {
+    trace_dump();
     AK_CUDA(cudaStreamSynchronize(ctx_->stream));
     return AK_OK;
+}
+
+float Runner::last_step_gpu_ms() {
+    if (!ev_g_valid_) return 0.0f;
+    ev_g_valid_ = false;
+    float ms = 0.0f;
+    if (cudaEventElapsedTime(&ms, ev_g0_, ev_g1_) != cudaSuccess) {
+        cudaGetLastError();
+        return 0.0f;
+    }
+    return ms;
 }
 
 float Runner::last_attn_ms() {

@@ -100,6 +100,8 @@ class Runner {
     void enable_attn_timing(bool on) { attn_timing_ = on; }
     void set_keep_logits(bool on) { keep_logits_ = on; }
     float last_attn_ms();
+    float last_step_gpu_ms();          // device time of the last captured step (attn timing on)
+    double launch_host_ms = 0.0;       // host time spent inside cudaGraphLaunch, accumulated
     uint64_t graph_launches = 0, eager_steps = 0;
     uint64_t h2d_bytes = 0, d2h_bytes = 0;   // bytes copied by run() / run_decode_graph()
     uint64_t graph_kernels = 0;              // kernel launches recorded in the captured decode step
@@ -143,7 +145,17 @@ class Runner {
     };
     std::map<uint64_t, StepGraph> graphs_;  // key = (prefill row bucket << 32) | prefill sequence bucket
     bool attn_timing_ = false;
-    cudaEvent_t ev_attn0_ = nullptr, ev_attn1_ = nullptr;
+    cudaEvent_t ev_attn0_ = nullptr, ev_attn1_ = nullptr, ev_g0_ = nullptr, ev_g1_ = nullptr;
+    bool ev_g_valid_ = false;
+    // AK_TRACE=1 (eager steps only): one event after every launch, per-launch times to stderr
+    std::vector<cudaEvent_t> trace_ev_;
+    std::vector<const char*> trace_lbl_;
+    size_t trace_n_ = 0;
+    std::vector<cudaEvent_t> gtrace_ev_;      // the same inside the captured decode step (event-record nodes)
+    std::vector<const char*> gtrace_lbl_;
+    bool gtrace_capture_ = false, gtrace_ran_ = false;
+    void trace_mark(const char* label);
+    void trace_dump();
     bool ev_valid_ = false;
 };
 

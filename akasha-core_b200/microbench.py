@@ -165,7 +165,9 @@ def bench_engine(ak, torch, iters, small):
     out = {"kernel": "engine decode step (162M, 64 seqs)", "ms_per_step": dt * 1e3, "tok/s": 64 / dt,
            "kernels_per_step": st["kernel_launches"] / max(1, st["steps"]),
            "attn_us_layer0": 1e3 * st["attn_ms_total"] / max(1, st["attn_launches_timed"]),
-           "attn_GB/s": st["attn_bytes_total"] / max(1e-9, st["attn_ms_total"] * 1e-3) / 1e9}
+           "attn_GB/s": st["attn_bytes_total"] / max(1e-9, st["attn_ms_total"] * 1e-3) / 1e9,
+           "gpu_ms_per_step": st["step_gpu_ms_total"] / max(1, st["steps"]),
+           "graph_launch_host_ms_per_step": st["launch_host_ms_total"] / max(1, st["graph_launches"])}
     if mixed:
         out["mixed_step_ms"] = mixed   # first entry includes the bucket's graph capture
     eng.close(); w.close(); ctx.close()

@@ -267,7 +267,6 @@ def main():
                          # DRAM bytes per launch: 1.059 x the algorithmic bytes, the ratio ncu measured
                          # (dram__bytes_read.sum + dram__bytes_write.sum) on a smaller launch of the same
                          # kernel; traffic grows in proportion to the K/V bytes
-                         # (profiles/attn_decode_paged_bf16_hd64_ncu.md)
                          "traffic": 1.059 * attn_bytes,
                          "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "launches_timed": st["attn_launches_timed"]},
             "clocks": clocks,

@@ -326,6 +326,8 @@ typedef struct ak_engine_stats {
     uint64_t attn_launches_timed;
     uint64_t attn_bytes_total;   /* algorithmic bytes of those launches */
     uint64_t h2d_bytes, d2h_bytes; /* bytes the engine copied host->device / device->host */
+    double step_gpu_ms_total;      /* device time of the captured steps (attn_timing) */
+    double launch_host_ms_total;   /* host time spent launching the captured steps */
 } ak_engine_stats;
 AK_API int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out);
 AK_API int ak_engine_reset_stats(ak_engine* e);
