@@ -127,6 +127,8 @@ _PROTOS = {
     "ak_weights_set_param": [vp, C.c_uint32, f32p, C.c_uint64],
     "ak_weights_get_param": [vp, C.c_uint32, f32p, C.c_uint64],
     "ak_weights_init_synthetic": [vp, C.c_uint64, C.c_float],
+    "ak_akv3_read_header": [C.c_char_p, C.POINTER(_ModelConfig), C.POINTER(C.c_uint64)],
+    "ak_weights_load_akv3": [vp, C.c_char_p, C.POINTER(C.c_uint64)],
     "ak_session_create": [vp, vp, C.c_uint32, C.POINTER(vp)],
     "ak_session_destroy": [vp],
     "ak_session_attach_cache": [vp],
@@ -248,6 +250,34 @@ class ModelConfig:
         return sum(int(np.prod(s)) for s in self.param_shapes())
 
 
+def akv3_read_header(path: str):
+    """(ModelConfig, train_step) of an AKV3 checkpoint file."""
+    c, ts = _ModelConfig(), C.c_uint64(0)
+    check(lib().ak_akv3_read_header(path.encode(), C.byref(c), C.byref(ts)))
+    return ModelConfig(c.vocab_size, c.dim, c.num_heads, c.num_layers, c.seq_len, c.ffn_hidden, c.norm_eps, c.eos_token), ts.value
+
+
+def akv3_write(path: str, cfg: "ModelConfig", params, train_step: int = 0, schedule_step: int = 0, moments=()):
+    """Write an AKV3 file exactly as `checkpoint::save` lays it out (src/nn/checkpoint.rs:49-95).
+    For tests and for exporting synthetic weights to the reference."""
+    import struct
+    with open(path, "wb") as f:
+        f.write(b"AKV3")
+        f.write(struct.pack("<IIIQIIQI", cfg.vocab_size, cfg.dim, cfg.num_heads, cfg.num_layers, cfg.seq_len,
+                            cfg.ffn_hidden, train_step, schedule_step))
+        f.write(struct.pack("<Q", len(params)))
+        for p in params:
+            a = np.ascontiguousarray(p, np.float32)
+            f.write(struct.pack("<Q", a.size))
+            f.write(a.tobytes())
+        f.write(struct.pack("<Q", len(moments)))
+        for m, v in moments:
+            for t in (m, v):
+                a = np.ascontiguousarray(t, np.float32)
+                f.write(struct.pack("<Q", a.size))
+                f.write(a.tobytes())
+
+
 # ------------------------------------------------------------------ synthetic inputs
 def _splitmix64(z: np.ndarray) -> np.ndarray:
     z = (z + np.uint64(0x9E3779B97F4A7C15)).astype(np.uint64)
@@ -356,6 +386,12 @@ class ModelWeights:
         for i, p in enumerate(params):
             a = np.ascontiguousarray(p, np.float32)
             check(lib().ak_weights_set_param(self.h, i, a.ctypes.data_as(f32p), a.size))
+
+    def load_akv3(self, path: str) -> int:
+        """`checkpoint::load` (src/nn/checkpoint.rs:98-161): weights from an AKV3 file; returns train_step."""
+        ts = C.c_uint64(0)
+        check(lib().ak_weights_load_akv3(self.h, path.encode(), C.byref(ts)))
+        return ts.value
 
     def init_synthetic(self, seed=0, std=0.02):
         check(lib().ak_weights_init_synthetic(self.h, seed, std))

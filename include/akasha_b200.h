@@ -261,6 +261,12 @@ AK_API int ak_weights_get_param(ak_weights* w, uint32_t index, float* host, uint
  * norm gains ~ N(1, std). Deterministic in (seed, index, element). For benchmarks. */
 AK_API int ak_weights_init_synthetic(ak_weights* w, uint64_t seed, float std);
 
+/* AKV3 checkpoints (src/nn/checkpoint.rs:18-36, 98-161): read the architecture header, and load
+ * the weight tensors of a file into `w` (architecture and every tensor length are checked first,
+ * as the reference's `load` does; the optimizer moments in the file are skipped). */
+AK_API int ak_akv3_read_header(const char* path, ak_model_config* cfg_out, uint64_t* train_step_out);
+AK_API int ak_weights_load_akv3(ak_weights* w, const char* path, uint64_t* train_step_out);
+
 /* InferenceSession::new (src/nn/inference.rs:25-40). The cache is created with the session
  * but DETACHED, as in the reference (`cache: None`): prefill returns AK_NO_CACHE until
  * ak_session_attach_cache or ak_session_generate_greedy attaches it. */
