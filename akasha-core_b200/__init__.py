@@ -108,6 +108,7 @@ _PROTOS = {
     "ak_flash_attention": [vp, vp, vp, vp, vp, vp, FlashAttnMeta],
     "ak_silu": [vp, vp, C.c_uint32],
     "ak_argmax": [vp, vp, C.c_uint32, C.c_uint32, vp],
+    "ak_sample_token": [vp, vp, C.c_uint32, C.c_uint32, vp, vp, C.c_float, C.c_float, C.c_uint32, C.c_float, C.c_uint64, C.c_uint64, vp],
     "ak_attn_decode_paged": [vp, vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
     "ak_attn_decode_paged_noalloc": [vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
     "ak_rope_kv_append": [vp, vp, vp, vp, vp, vp, vp] + [C.c_uint32] * 5,

@@ -756,3 +756,142 @@ int ak_bf16_to_f32(void* stream, const void* src, float* dst, uint64_t n) {
 }
 
 }  // extern "C"
+
+// ============================================================================ on-device sampler
+// `sample_token` (src/nn/sampling.rs:18-81) on the device, one CTA per sequence: repetition
+// penalty over the distinct seen ids (divide positive logits, multiply the others), then
+// temperature / top-k / top-p sampling with the probabilities formed in f64 as the reference does.
+// The reference draws its uniform number from an unseeded generator (sampling.rs:73); here it comes
+// from a counter-based generator over (seed, step, row), so a run can be reproduced. Candidates
+// are ordered by (logit descending, index ascending); the reference's unstable sort leaves the
+// order of EQUAL logits unspecified. temperature <= 0 is the greedy argmax of the penalised logits.
+namespace ak {
+
+constexpr int SMP_THREADS = 1024;
+constexpr int SMP_MAX_K = 1024;
+
+__device__ __forceinline__ uint64_t smp_mix(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__global__ void __launch_bounds__(SMP_THREADS)
+sample_rows_kernel(const float* __restrict__ logits, uint32_t n, uint32_t ld, const uint32_t* __restrict__ seen,
+                   const uint32_t* __restrict__ seen_off, float penalty, float temperature, uint32_t top_k, float top_p,
+                   uint64_t seed, uint64_t step, const int32_t* __restrict__ row_active, uint32_t* __restrict__ out_idx) {
+    extern __shared__ float srow[];                       // n logits, then the seen-id bitmap
+    uint32_t* bits = reinterpret_cast<uint32_t*>(srow + n);
+    __shared__ float wv[32];
+    __shared__ uint32_t wi[32];
+    __shared__ float cand_v[SMP_MAX_K];
+    __shared__ uint32_t cand_i[SMP_MAX_K];
+    const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (row_active && row_active[row] < 0) return;
+    const float* l = logits + (size_t)row * ld;
+    const uint32_t nwords = (n + 31) / 32;
+    for (uint32_t i = tid; i < nwords; i += SMP_THREADS) bits[i] = 0u;
+    for (uint32_t i = tid; i < n; i += SMP_THREADS) srow[i] = l[i];
+    __syncthreads();
+    if (penalty != 1.0f && seen) {
+        for (uint32_t i = seen_off[row] + tid; i < seen_off[row + 1]; i += SMP_THREADS) {
+            uint32_t id = seen[i];
+            if (id < n) atomicOr(&bits[id >> 5], 1u << (id & 31));
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < n; i += SMP_THREADS)
+            if (bits[i >> 5] & (1u << (i & 31))) srow[i] = srow[i] > 0.0f ? srow[i] / penalty : srow[i] * penalty;
+        __syncthreads();
+    }
+    const uint32_t k = (temperature <= 0.0f) ? 1u : top_k;
+    for (uint32_t c = 0; c < k; c++) {
+        float best = -INFINITY;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t i = tid; i < n; i += SMP_THREADS) {
+            float v = srow[i];
+            if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            argmax_combine(best, bi, ov, oi);
+        }
+        if (lane == 0) { wv[warp] = best; wi[warp] = bi; }
+        __syncthreads();
+        if (warp == 0) {
+            best = wv[lane];
+            bi = wi[lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                argmax_combine(best, bi, ov, oi);
+            }
+            if (lane == 0) {
+                cand_v[c] = best;
+                cand_i[c] = bi;
+                if (bi != 0xffffffffu) srow[bi] = -INFINITY;  // taken
+            }
+        }
+        __syncthreads();
+    }
+    if (tid != 0) return;
+    if (temperature <= 0.0f) { out_idx[row] = cand_i[0] == 0xffffffffu ? 0u : cand_i[0]; return; }
+    // candidates that ran out (-inf everywhere) end the list
+    uint32_t m = 0;
+    while (m < k && cand_i[m] != 0xffffffffu) m++;
+    if (m == 0) { out_idx[row] = 0; return; }
+    // f64 softmax over the candidates, reusing srow as f64 scratch is not possible (taken marks):
+    // k <= 1024 doubles are recomputed on the fly instead of stored.
+    const double mx = (double)cand_v[0], T = (double)temperature;
+    double sum = 0.0;
+    for (uint32_t j = 0; j < m; j++) sum += exp(((double)cand_v[j] - mx) / T);
+    uint32_t keep = m;
+    if (top_p < 1.0f) {
+        double cum = 0.0;
+        for (uint32_t j = 0; j < m; j++) {
+            cum += exp(((double)cand_v[j] - mx) / T) / sum;
+            if (cum >= (double)top_p) { keep = j + 1; break; }
+        }
+    }
+    double s2 = 0.0;
+    for (uint32_t j = 0; j < keep; j++) s2 += exp(((double)cand_v[j] - mx) / T) / sum;
+    const uint64_t bitsr = smp_mix(seed ^ smp_mix(step * 0x632BE59BD9B4E019ull + row + 1));
+    double r = (double)(bitsr >> 11) * (1.0 / 9007199254740992.0);  // [0, 1)
+    uint32_t pick = cand_i[keep - 1];
+    for (uint32_t j = 0; j < keep; j++) {
+        double p = (exp(((double)cand_v[j] - mx) / T) / sum) / s2;
+        if (r < p) { pick = cand_i[j]; break; }
+        r -= p;
+    }
+    out_idx[row] = pick;
+}
+
+int launch_sample_rows(cudaStream_t st, const float* logits, uint32_t rows, uint32_t n, uint32_t ld, const uint32_t* seen,
+                       const uint32_t* seen_off, float penalty, float temperature, uint32_t top_k, float top_p, uint64_t seed,
+                       uint64_t step, const int32_t* row_active, uint32_t* out_idx) {
+    if (rows == 0 || n == 0) return AK_OK;
+    AK_REQUIRE(temperature <= 0.0f || (top_k >= 1 && top_k <= SMP_MAX_K), AK_ERR_UNSUPPORTED,
+               "sampler: top_k must be in 1..%d on the device (got %u); top_k = 0 (no truncation) needs a full sort", SMP_MAX_K, top_k);
+    const size_t smem = (size_t)n * 4 + (size_t)((n + 31) / 32) * 4;
+    AK_REQUIRE(smem <= 214 * 1024, AK_ERR_UNSUPPORTED, "sampler: vocabulary of %u does not fit shared memory", n);
+    AK_CUDA(cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sample_rows_kernel<<<rows, SMP_THREADS, smem, st>>>(logits, n, ld, seen, seen_off, penalty, temperature, top_k, top_p, seed, step,
+                                                        row_active, out_idx);
+    AK_COUNT_LAUNCH();
+    AK_CHECK_LAUNCH();
+    return AK_OK;
+}
+
+}  // namespace ak
+
+extern "C" int ak_sample_token(void* stream, const float* logits, uint32_t rows, uint32_t n, const uint32_t* seen,
+                               const uint32_t* seen_off, float repetition_penalty, float temperature, uint32_t top_k, float top_p,
+                               uint64_t seed, uint64_t step, uint32_t* out_idx) {
+    AK_REQUIRE(logits && out_idx, AK_ERR_INVALID_ARG, "ak_sample_token: null pointer");
+    AK_REQUIRE(repetition_penalty == 1.0f || (seen && seen_off), AK_ERR_INVALID_ARG, "ak_sample_token: a repetition penalty needs the seen ids");
+    return ak::launch_sample_rows(ak::as_stream(stream), logits, rows, n, n, seen, seen_off, repetition_penalty, temperature, top_k,
+                                  top_p, seed, step, nullptr, out_idx);
+}

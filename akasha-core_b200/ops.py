@@ -82,6 +82,26 @@ def argmax(logits, rows, n, out_idx, stream=None):  # src/nn/sampling.rs:83-91 o
     check(lib().ak_argmax(_s(stream), _p(logits), rows, n, _p(out_idx)))
 
 
+def sample_token(logits, rows, n, out_idx, temperature, top_k, top_p, seed, step, seen=None, seen_off=None,
+                 repetition_penalty=1.0, stream=None):
+    """`sample_token` (src/nn/sampling.rs:18-81) on the device; see the header for the RNG contract."""
+    check(lib().ak_sample_token(_s(stream), _p(logits), rows, n, _p(seen), _p(seen_off), repetition_penalty, temperature,
+                                top_k, top_p, seed, step, _p(out_idx)))
+
+
+def sampler_uniform(seed: int, step: int, row: int) -> float:
+    """The uniform number the device sampler draws for (seed, step, row)."""
+    M = (1 << 64) - 1
+
+    def mix(z):
+        z = (z + 0x9E3779B97F4A7C15) & M
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M
+        return z ^ (z >> 31)
+    b = mix(seed ^ mix((step * 0x632BE59BD9B4E019 + row + 1) & M))
+    return (b >> 11) / 9007199254740992.0
+
+
 # ---- fused sm_100a kernels -----------------------------------------------------------------
 def attn_decode_scratch_bytes(rows, heads, head_dim, max_blocks_per_seq, n_splits=0, kv_dtype=AK_BF16):
     p = AttnDecodeParams(rows, heads, head_dim, 16, max_blocks_per_seq, 0.0, kv_dtype, n_splits, 0)

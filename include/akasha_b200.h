@@ -147,6 +147,16 @@ AK_API int ak_silu(void* stream, float* x, uint32_t n);
  * logits the FIRST index holding the maximum. out_idx: device uint32[rows]. */
 AK_API int ak_argmax(void* stream, const float* logits, uint32_t rows, uint32_t n, uint32_t* out_idx);
 
+/* sampling::sample_token (src/nn/sampling.rs:18-81) on the device, one row per sequence:
+ * repetition penalty over the DISTINCT ids of seen[seen_off[r] .. seen_off[r+1]) (positive logits
+ * divided, the others multiplied), then temperature / top-k / top-p with f64 probabilities.
+ * temperature <= 0 is greedy. top_k must be 1..1024 when sampling. The uniform draw is
+ * splitmix64(seed, step, row) (the reference uses an unseeded generator); equal logits are ordered
+ * by index (the reference's unstable sort leaves that order open). */
+AK_API int ak_sample_token(void* stream, const float* logits, uint32_t rows, uint32_t n, const uint32_t* seen,
+                           const uint32_t* seen_off, float repetition_penalty, float temperature, uint32_t top_k, float top_p,
+                           uint64_t seed, uint64_t step, uint32_t* out_idx);
+
 /* ---- new fused sm_100a kernels (no single-emitter counterpart in the reference) ---- */
 
 /* Ragged paged decode attention: fuses attn_qk_cached + softmax_rect + attn_av_cached

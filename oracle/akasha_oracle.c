@@ -291,6 +291,52 @@ OR_EXPORT uint32_t or_sample_greedy(const float* logits, uint32_t n, const uint3
     return r;
 }
 
+/* src/nn/sampling.rs:18-81 with the uniform draw `r` supplied by the caller (the reference
+ * calls an unseeded rand::random, sampling.rs:73). Candidates are ordered by logit descending;
+ * equal logits by index ascending (the reference's sort_unstable_by leaves ties unspecified). */
+typedef struct { float v; uint32_t i; } or_cand;
+static int or_cand_cmp(const void* a, const void* b) {
+    const or_cand* x = (const or_cand*)a; const or_cand* y = (const or_cand*)b;
+    if (x->v > y->v) return -1;
+    if (x->v < y->v) return 1;
+    return (x->i > y->i) - (x->i < y->i);
+}
+OR_EXPORT uint32_t or_sample_token(const float* logits, uint32_t n, float temperature, uint32_t top_k, float top_p,
+                                   const uint32_t* seen, uint32_t n_seen, float penalty, double r) {
+    float* l = (float*)malloc((size_t)n * 4);
+    memcpy(l, logits, (size_t)n * 4);
+    if (penalty != 1.0f) {
+        uint8_t* mark = (uint8_t*)calloc(n, 1);
+        for (uint32_t i = 0; i < n_seen; i++)
+            if (seen[i] < n) mark[seen[i]] = 1;
+        for (uint32_t i = 0; i < n; i++)
+            if (mark[i]) l[i] = (l[i] > 0.0f) ? l[i] / penalty : l[i] * penalty;
+        free(mark);
+    }
+    if (temperature <= 0.0f) { uint32_t a = or_argmax(l, n); free(l); return a; }
+    or_cand* c = (or_cand*)malloc(sizeof(or_cand) * n);
+    for (uint32_t i = 0; i < n; i++) { c[i].v = l[i]; c[i].i = i; }
+    qsort(c, n, sizeof(or_cand), or_cand_cmp);
+    uint32_t m = n;
+    if (top_k > 0 && top_k < n) m = top_k;
+    double* p = (double*)malloc(sizeof(double) * m);
+    double mx = (double)c[0].v, sum = 0.0;
+    for (uint32_t j = 0; j < m; j++) { p[j] = exp(((double)c[j].v - mx) / (double)temperature); sum += p[j]; }
+    for (uint32_t j = 0; j < m; j++) p[j] /= sum;
+    if (top_p < 1.0f) {
+        double cum = 0.0; uint32_t keep = m;
+        for (uint32_t j = 0; j < m; j++) { cum += p[j]; if (cum >= (double)top_p) { keep = j + 1; break; } }
+        m = keep;
+        double s = 0.0;
+        for (uint32_t j = 0; j < m; j++) s += p[j];
+        for (uint32_t j = 0; j < m; j++) p[j] /= s;
+    }
+    uint32_t pick = c[m - 1].i;
+    for (uint32_t j = 0; j < m; j++) { if (r < p[j]) { pick = c[j].i; break; } r -= p[j]; }
+    free(p); free(c); free(l);
+    return pick;
+}
+
 /* ---------------------------------------------------------------- model + session */
 
 typedef struct {

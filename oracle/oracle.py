@@ -59,6 +59,8 @@ def lib() -> C.CDLL:
         L.or_argmax.restype = C.c_uint32
         L.or_sample_greedy.argtypes = [f32p, C.c_uint32, u32p, C.c_uint32, C.c_float]
         L.or_sample_greedy.restype = C.c_uint32
+        L.or_sample_token.argtypes = [f32p, C.c_uint32, C.c_float, C.c_uint32, C.c_float, u32p, C.c_uint32, C.c_float, C.c_double]
+        L.or_sample_token.restype = C.c_uint32
         L.or_model_create.argtypes = [C.c_uint32] * 5 + [C.c_float, C.POINTER(f32p), C.c_int]
         L.or_model_create.restype = C.c_void_p
         L.or_model_destroy.argtypes = [C.c_void_p]
@@ -215,6 +217,13 @@ def sample_greedy(logits, seen=(), penalty=1.0) -> int:
     logits = np.ascontiguousarray(logits, np.float32)
     seen = np.ascontiguousarray(seen, np.uint32)
     return int(lib().or_sample_greedy(_f(logits), logits.size, _u(seen), seen.size, penalty))
+
+
+def sample_token(logits, temperature, top_k, top_p, seen=(), penalty=1.0, r=0.5) -> int:
+    """`sample_token` (src/nn/sampling.rs:18-81) with the uniform draw r supplied."""
+    logits = np.ascontiguousarray(logits, np.float32)
+    seen = np.ascontiguousarray(seen, np.uint32)
+    return int(lib().or_sample_token(_f(logits), logits.size, temperature, top_k, top_p, _u(seen), seen.size, penalty, r))
 
 
 class Model:
