@@ -92,7 +92,14 @@ int launch_attn_prefill_paged(cudaStream_t st, const void* q, const void* k_pool
                               const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
                               const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len,
                               uint32_t row_base, uint32_t heads, uint32_t head_dim, uint32_t block_size,
-                              float scale, uint32_t dtype);
+                              float scale, uint32_t dtype, uint64_t q_rows, uint64_t pool_blocks);
+// ---- attn_prefill_tc.cu: the same contract on the tensor cores (bf16, head_dim 64/128). q has
+// q_rows rows of heads*head_dim; the pools hold pool_blocks blocks. Waits that expire set a status word.
+int launch_attn_prefill_tc(cudaStream_t st, const void* q, uint64_t q_rows, const void* k_pool, const void* v_pool,
+                           uint64_t pool_blocks, const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
+                           const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base, uint32_t heads,
+                           uint32_t head_dim, float scale);
+int prefill_tc_status(unsigned int* out);
 // The reference emitter's contiguous form (f32 q/k/v [*,dim], optional l_cache).
 int launch_flash_attention_f32(cudaStream_t st, const float* q, const float* k, const float* v, float* out,
                                float* l_cache, ak_flash_attn_meta m);

@@ -395,7 +395,7 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
         }
         if (n_pf_seqs) {
             RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
-                                         d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt));
+                                         d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
         }
         if (tp) {
             RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));

@@ -146,6 +146,9 @@ int ak_check_device_status(void* stream) {
     rc = attn_decode_status(&v);
     if (rc) return rc;
     AK_REQUIRE(v == 0, AK_ERR_DEVICE_WAIT, "attn_decode_paged: a bounded device-side wait expired (code %u)", v);
+    rc = prefill_tc_status(&v);
+    if (rc) return rc;
+    AK_REQUIRE(v == 0, AK_ERR_DEVICE_WAIT, "attn_prefill (tensor cores): a bounded device-side wait expired (code %u)", v);
     return AK_OK;
 }
 

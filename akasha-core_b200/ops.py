@@ -130,6 +130,15 @@ def attn_decode_noalloc_max_scratch_bytes() -> int:
     return int(lib().ak_attn_decode_noalloc_max_scratch_bytes())
 
 
+def attn_prefill_paged(q, k_pool, v_pool, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, q_rows,
+                       heads, head_dim, scale, dtype=AK_BF16, pool_blocks=0, stream=None):
+    """Causal attention of a ragged batch of newly prefilled sequences over the paged pools
+    (the prefill graph's FLASH_ATTENTION node, src/nn/inference_graphs.rs:271-285)."""
+    check(lib().ak_attn_prefill_paged(_s(stream), _p(q), _p(k_pool), _p(v_pool), _p(block_tables), max_blocks_per_seq, _p(cu),
+                                      _p(seq_slot), _p(out), n_seqs, max_len, q_rows, heads, head_dim, scale, dtype,
+                                      pool_blocks))
+
+
 def rope_kv_append(qkv, positions, slots, q_out, k_pool, v_pool, tokens, heads, head_dim, kv_dtype=AK_BF16,
                    stream=None):
     check(lib().ak_rope_kv_append(_s(stream), _p(qkv), _p(positions), _p(slots), _p(q_out), _p(k_pool), _p(v_pool),

@@ -209,6 +209,19 @@ AK_API int ak_rope_kv_append(void* stream, const float* qkv, const int32_t* posi
                              void* q_out, void* k_pool, void* v_pool, uint32_t tokens, uint32_t heads,
                              uint32_t head_dim, uint32_t block_size, uint32_t kv_dtype);
 
+/* Causal attention of newly prefilled sequences over the paged KV pools: the prefill graph's
+ * FLASH_ATTENTION node (src/nn/inference_graphs.rs:271-285, kernel src/shaders/cuda.rs:633-685)
+ * for a ragged batch. Rows [cu[i], cu[i+1]) of q/out belong to sequence i (query j at position
+ * j); its K/V are read through block_tables[seq_slot[i]] (max_blocks_per_seq entries per slot).
+ *   q, out [q_rows, heads*head_dim] and the pools [pool_blocks, heads, 16, head_dim], all `dtype`.
+ * bf16 with head_dim 64/128 runs on the tensor cores (tcgen05.mma, TMEM accumulators, TMA);
+ * q must then be 16-byte aligned. Other shapes and f32 use the CUDA-core kernel. */
+AK_API int ak_attn_prefill_paged(void* stream, const void* q, const void* k_pool, const void* v_pool,
+                                 const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
+                                 const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len,
+                                 uint32_t q_rows, uint32_t heads, uint32_t head_dim, float scale, uint32_t dtype,
+                                 uint32_t pool_blocks);
+
 /* One kernel: h = x (+ residual, written back to x when given), y = rmsnorm(h) * w, then an
  * optional RoPE of y (adjacent pairs per head, positions[row]; head_dim = 0 disables).
  * y is f32 or bf16 (out_dtype). */

@@ -189,3 +189,51 @@ def test_gemm_bf16_epilogues(ak, orc, torch_cuda, epi, m, n, k):
     ak.ops.gemm_bf16(da, wt, c, m, n, k, epi)
     torch.cuda.synchronize()
     assert np.max(np.abs(host(c) - want)) < tol
+
+
+def ref_prefill(orc, q, k, v, hd):
+    """Causal attention of one sequence (q/k/v [L, dim]) with the oracle's flash attention."""
+    return orc.flash_attention(np.ascontiguousarray(q), np.ascontiguousarray(k), np.ascontiguousarray(v), hd)
+
+
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("heads,hd,lens", [
+    (12, 64, [33]),                                        # the reference's flash-attention test length
+    (12, 64, [1, 15, 16, 17, 63, 64, 65, 127, 128, 129, 232, 448]),
+    (2, 64, [700, 3, 0, 257]),                             # several 128-query tiles, an empty sequence
+    (16, 128, [5, 130, 300]),
+    (2, 128, [1000]),
+    (4, 8, [6, 33]),                                       # generic head_dim path
+])
+def test_attn_prefill_paged(ak, orc, torch_cuda, dtype, heads, hd, lens):
+    """Ragged causal prefill attention over the paged pools (bf16 head_dim 64/128: the tcgen05 kernel)."""
+    torch = torch_cuda
+    dim = heads * hd
+    kp, vp, tables, ks, vs, n_blocks, max_blocks = build_paged(torch, orc, lens, heads, hd, dtype, seed=5)
+    cu = np.zeros(len(lens) + 1, np.int32)
+    cu[1:] = np.cumsum(lens)
+    total = int(cu[-1])
+    q = orc.lcg(total * dim, 11).reshape(total, dim) * 2.0
+    if dtype == 1:
+        q = orc.round_bf16(q)
+    tdt = torch.float32 if dtype == 0 else torch.bfloat16
+    q_rows = total + 5                                     # rows past the batch stay untouched
+    dq = torch.zeros(q_rows, dim, device="cuda", dtype=tdt)
+    dq[:total] = torch.from_numpy(q).cuda().to(tdt)
+    out = torch.full((q_rows, dim), float("nan"), device="cuda", dtype=tdt)
+    seq_slot = torch.arange(len(lens), dtype=torch.int32, device="cuda")
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    ak.ops.attn_prefill_paged(dq, kp, vp, tables, max_blocks, torch.from_numpy(cu).cuda(), seq_slot, out, len(lens), max(lens),
+                              q_rows, heads, hd, scale, dtype, n_blocks)
+    torch.cuda.synchronize()
+    ak.check(ak.lib().ak_check_device_status(None))
+    got = host(out)
+    assert np.isnan(got[total:]).all(), "rows outside the batch were written"
+    tol = 3e-5 if dtype == 0 else 1.2e-2   # bf16: P and the output are rounded to 8 bits of mantissa
+    for i, L in enumerate(lens):
+        if L == 0:
+            continue
+        want = ref_prefill(orc, q[cu[i]:cu[i + 1]], ks[i], vs[i], hd)
+        g = got[cu[i]:cu[i + 1]]
+        assert np.isfinite(g).all(), "NaN leaked from masked or unwritten cache slots"
+        assert np.max(np.abs(g - want)) < tol, (i, L)
