@@ -173,7 +173,11 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
 template <int BN, int EPI>
 __global__ void __launch_bounds__(G_THREADS)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmEpi ep,
-                 uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols) {
+                 uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols, uint32_t a_rows, uint32_t kil) {
+    // kil: the 64/16 = 4 MMAs of a K block are dealt round-robin to kil accumulators (per K segment), so
+    // consecutive MMAs do not wait on one another's accumulator; the epilogue adds the accumulators in order.
+    // a_rows: rows of the activation box (128, or fewer when m is small: the MMA still reads 128 rows of
+    // the stage, the rows past the box hold stale data and feed accumulator rows that are never stored).
     // kseg > 1 (only with a cluster of one CTA): the K range is accumulated in kseg separate TMEM
     // accumulators that the epilogue adds in order. It reproduces, bit for bit, what a cluster of
     // kseg CTAs computes for the same (n, k), so a row's result does not depend on how many rows
@@ -229,9 +233,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // requested BEFORE waiting for it, so the weight stream from HBM overlaps the
             // predecessor's tail. The activation tiles follow after the wait.
             const uint32_t pre = num_kb < stages ? num_kb : stages;
+            const uint32_t stage_tx = a_rows * (GB_K * 2) + C::B_BYTES;
             for (uint32_t i = 0; i < pre; i++) {
                 uint8_t* b_dst = smem + (size_t)i * C::STAGE_BYTES + C::A_BYTES;
-                mbar_expect_tx(&full_bar[i], C::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[i], stage_tx);
                 tma_load_2d(b_dst, &tmB, (int32_t)((kb_begin + i) * GB_K), (int32_t)n0, &full_bar[i]);
             }
             pdl_wait();
@@ -242,7 +247,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); break; }
                 uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
                 uint8_t* b_dst = a_dst + C::A_BYTES;
-                mbar_expect_tx(&full_bar[s], C::STAGE_BYTES);
+                mbar_expect_tx(&full_bar[s], stage_tx);
                 const int32_t kx = (int32_t)((kb_begin + i) * GB_K);
                 tma_load_2d(a_dst, &tmA, kx, (int32_t)m0, &full_bar[s]);
                 tma_load_2d(b_dst, &tmB, kx, (int32_t)n0, &full_bar[s]);
@@ -264,8 +269,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (uint32_t kk = 0; kk < GB_K / 16; kk++) {
                     // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the address field
-                    tc_mma_f16(tmem_base + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                               (first_of_seg && kk == 0) ? 0u : 1u);
+                    tc_mma_f16(tmem_base + (seg * kil + (kk & (kil - 1))) * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                               (first_of_seg && kk < kil) ? 0u : 1u);
                 }
                 tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
             }
@@ -299,7 +304,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-                    for (uint32_t seg = 1; seg < kseg; seg++) {  // segment order = cluster rank order
+                    for (uint32_t seg = 1; seg < kseg * kil; seg++) {  // segment order = cluster rank order
                         tmem_ld16(tmem_base + ((quad * 32u) << 16) + seg * BN + c0, r);
                         tmem_ld_wait();
 #pragma unroll
@@ -334,6 +339,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (num_kb > 0) {
                     tmem_ld16(tmem_base + ((quad * 32u) << 16) + c0, r);
                     tmem_ld_wait();
+                    for (uint32_t a = 1; a < kil; a++) {
+                        uint32_t r2[16];
+                        tmem_ld16(tmem_base + ((quad * 32u) << 16) + a * BN + c0, r2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++) r[j] = 0u;
@@ -383,6 +395,13 @@ struct GemmPlan {
 static constexpr uint32_t SMEM_TWO_PER_SM = 112 * 1024;   // two CTAs fit one SM below this
 static constexpr uint32_t SMEM_ONE_PER_SM = 220 * 1024;
 
+// Rows of the activation TMA box: a decode batch fills only part of the 128-row MMA tile, and rows the
+// box does not fetch cost neither L2 requests nor zero-fill writes.
+static uint32_t a_box_rows(uint32_t m) {
+    static const bool full = [] { const char* e = getenv("AK_GEMM_FULLBOX"); return e && e[0] == '1'; }();
+    if (full || m > 64) return GB_M;
+    return m > 32 ? 64 : (m > 16 ? 32 : 16);
+}
 static uint32_t stage_bytes(uint32_t bn) { return GB_M * GB_K * 2 + bn * GB_K * 2; }
 
 // Skinny problems (m <= 128: decode batches) are latency- and weight-stream-bound: pick the
@@ -452,9 +471,18 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             const bool better = per < best_kb || (per == best_kb && ctas > best_ctas);
             if (better) { best_kb = per; best_ctas = ctas; p.bn = bn; p.ks = ks; }
         }
+    uint32_t force_st = 0;
+    if (const char* e = getenv("AK_GEMM_PLAN")) {  // tuning aid: "bn,ks,stages" for the skinny plan
+        unsigned b = 0, s2 = 0, t = 0;
+        if (sscanf(e, "%u,%u,%u", &b, &s2, &t) == 3 && (b == 16 || b == 32 || b == 64) && (s2 == 1 || s2 == 2 || s2 == 4 || s2 == 8) &&
+            (s2 == 1 || (allow_split && (b / s2) % 4 == 0 && s2 * 2 <= num_kb))) {
+            p.bn = b; p.ks = s2; force_st = t;
+        }
+    }
     const uint32_t per = cdiv(num_kb, p.ks);
     const uint32_t red = p.ks > 1 ? GB_M * p.bn * 4 : 0;
     uint32_t st = (SMEM_TWO_PER_SM - 1024 - red) / stage_bytes(p.bn);
+    if (force_st && force_st < st) st = force_st;
     if (st > G_MAX_STAGES) st = G_MAX_STAGES;
     if (st < 2) st = 2;
     p.stages = st < per ? st : (per ? per : 1);
@@ -473,18 +501,22 @@ static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap
         AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
         attr_set[dev & 63] = SMEM_ONE_PER_SM;
     }
-    uint32_t need = p.kseg * BN, cols = 32;
+    uint32_t kil = 1;
+    if (const char* e = getenv("AK_GEMM_KIL")) kil = (uint32_t)atoi(e);
+    if (kil != 2 && kil != 4) kil = 1;
+    while (kil > 1 && p.kseg * kil * BN > 512) kil /= 2;
+    uint32_t need = p.kseg * kil * BN, cols = 32;
     while (cols < need) cols *= 2;
     AK_REQUIRE(cols <= 512, AK_ERR_UNSUPPORTED, "gemm_bf16: %u accumulator columns exceed TMEM", need);
     return launch_k(gemm_bf16_kernel<BN, EPI>, dim3(cdiv(n, BN), cdiv(m, GB_M), p.ks), dim3(G_THREADS), smem, st, dim3(1, 1, p.ks),
-                    tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols);
+                    tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols, a_box_rows(m), kil);
 }
 
 template <int BN>
 static int launch_bn(cudaStream_t st, const void* a, const void* wt, const GemmEpi& ep, uint32_t m, uint32_t n, uint32_t k,
                      uint32_t epi, const GemmPlan& p) {
     CUtensorMap tmA, tmB;
-    int rc = make_tmap_2d(&tmA, a, 2, k, m, (uint64_t)k * 2, GB_K, GB_M, TMA_SWIZZLE_128B);
+    int rc = make_tmap_2d(&tmA, a, 2, k, m, (uint64_t)k * 2, GB_K, a_box_rows(m), TMA_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmB, wt, 2, k, n, (uint64_t)k * 2, GB_K, BN, TMA_SWIZZLE_128B);
     if (rc) return rc;

@@ -101,6 +101,45 @@ def bench_gemm(ak, torch, iters, small):
     return res
 
 
+def bench_skinny(ak, torch, iters, small):
+    """The four per-layer GEMMs of a 64-row decode step, each as a chain of 12 launches over 12
+    different weight sets (170 MB in total, more than L2) replayed from a CUDA graph, so that
+    each launch sees the launch-to-launch overlap and the cold weights it sees inside the engine.
+    `--plans "16,1,6;32,1,6"` repeats every shape under those skinny-plan overrides."""
+    M = int(_opt("--m", 64))
+    plans = [p for p in str(_opt("--plans", "")).split(";") if p]
+    shapes = [("qkv", 2304, 768, ak.EPI_STORE_F32), ("out", 768, 768, ak.EPI_ADD_F32),
+              ("up", 3072, 768, ak.EPI_SILU_BF16), ("down", 768, 3072, ak.EPI_ADD_F32)]
+    res = []
+    for name, N, K, epi in shapes:
+        a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+        wts = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(12)]
+        pad = [torch.empty(9 * 1024 * 1024 // 2, device="cuda", dtype=torch.bfloat16) for _ in range(12)]  # spacing, as other layers' weights
+        c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if epi == ak.EPI_SILU_BF16 else torch.float32)
+        for plan in ([None] + plans):
+            if plan is None:
+                os.environ.pop("AK_GEMM_PLAN", None)
+            else:
+                os.environ["AK_GEMM_PLAN"] = plan
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                stream = side.cuda_stream
+                for wt in wts:
+                    ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, stream)
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(4):
+                        for wt in wts:
+                            ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, torch.cuda.current_stream().cuda_stream)
+                ms = timed(torch, g.replay, iters)
+            res.append({"kernel": "gemm_bf16_kernel chain", "op": name, "m": M, "n": N, "k": K, "plan": plan or "default",
+                        "us_per_launch": 1e3 * ms / 48})
+        os.environ.pop("AK_GEMM_PLAN", None)
+        del a, wts, c, pad
+    return res
+
+
 def bench_norm(ak, torch, iters, small):
     rows, size, hd = (8192 if small else 32768), 768, 64
     nbuf = 4  # rotate buffers: 4 x (100 MB in + 50 MB out) > L2
@@ -179,13 +218,13 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     ak = entry.load_package()
-    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine")]
+    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine", "skinny")]
     iters = int(_opt("--iters", 20))
     small = "--small" in sys.argv
     which = args or ["attn", "gemm", "norm"]
     torch.cuda.set_device(0)
     for w in which:
-        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine}[w](ak, torch, iters, small)
+        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine, "skinny": bench_skinny}[w](ak, torch, iters, small)
         for line in (r if isinstance(r, list) else [r]):
             print(json.dumps(line))
     torch.cuda.synchronize()
