@@ -173,9 +173,7 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
 template <int BN, int EPI>
 __global__ void __launch_bounds__(G_THREADS)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmEpi ep,
-                 uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols, uint32_t a_rows, uint32_t kil) {
-    // kil: the 64/16 = 4 MMAs of a K block are dealt round-robin to kil accumulators (per K segment), so
-    // consecutive MMAs do not wait on one another's accumulator; the epilogue adds the accumulators in order.
+                 uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols, uint32_t a_rows) {
     // a_rows: rows of the activation box (128, or fewer when m is small: the MMA still reads 128 rows of
     // the stage, the rows past the box hold stale data and feed accumulator rows that are never stored).
     // kseg > 1 (only with a cluster of one CTA): the K range is accumulated in kseg separate TMEM
@@ -269,8 +267,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                 for (uint32_t kk = 0; kk < GB_K / 16; kk++) {
                     // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the address field
-                    tc_mma_f16(tmem_base + (seg * kil + (kk & (kil - 1))) * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                               (first_of_seg && kk < kil) ? 0u : 1u);
+                    tc_mma_f16(tmem_base + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                               (first_of_seg && kk == 0) ? 0u : 1u);
                 }
                 tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
             }
@@ -304,7 +302,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
-                    for (uint32_t seg = 1; seg < kseg * kil; seg++) {  // segment order = cluster rank order
+                    for (uint32_t seg = 1; seg < kseg; seg++) {  // segment order = cluster rank order
                         tmem_ld16(tmem_base + ((quad * 32u) << 16) + seg * BN + c0, r);
                         tmem_ld_wait();
 #pragma unroll
@@ -339,13 +337,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 if (num_kb > 0) {
                     tmem_ld16(tmem_base + ((quad * 32u) << 16) + c0, r);
                     tmem_ld_wait();
-                    for (uint32_t a = 1; a < kil; a++) {
-                        uint32_t r2[16];
-                        tmem_ld16(tmem_base + ((quad * 32u) << 16) + a * BN + c0, r2);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(r2[j]));
-                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++) r[j] = 0u;
@@ -462,8 +453,11 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
     for (int bi = 0; bi < 3; bi++)
         for (int ki = 0; ki < 4; ki++) {
             const uint32_t bn = bns[bi], ks = kss[ki];
-            // a cluster exchange costs more than it saves on short K chains: split only K > 1024
-            if (ks > 1 && (!allow_split || num_kb <= 16 || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
+            // One MMA occupies the tensor core ~150 cycles whatever its N, so a CTA's main loop costs
+            // ~0.3 us per K block; a cluster exchange costs ~1.5 us. Split long K chains (K > 1024), and
+            // short ones only when the unsplit grid would cover less than half of the SMs.
+            const bool short_k_ok = cdiv(n, 16) * 2 <= 148;
+            if (ks > 1 && (!allow_split || (num_kb <= 16 && !short_k_ok) || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
             const uint32_t per = cdiv(num_kb, ks);
             if (ks > 1 && (ks - 1) * per >= num_kb) continue;  // every CTA of the cluster gets work
             const uint32_t ctas = cdiv(n, bn) * ks;
@@ -501,15 +495,11 @@ static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap
         AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
         attr_set[dev & 63] = SMEM_ONE_PER_SM;
     }
-    uint32_t kil = 1;
-    if (const char* e = getenv("AK_GEMM_KIL")) kil = (uint32_t)atoi(e);
-    if (kil != 2 && kil != 4) kil = 1;
-    while (kil > 1 && p.kseg * kil * BN > 512) kil /= 2;
-    uint32_t need = p.kseg * kil * BN, cols = 32;
+    uint32_t need = p.kseg * BN, cols = 32;
     while (cols < need) cols *= 2;
     AK_REQUIRE(cols <= 512, AK_ERR_UNSUPPORTED, "gemm_bf16: %u accumulator columns exceed TMEM", need);
     return launch_k(gemm_bf16_kernel<BN, EPI>, dim3(cdiv(n, BN), cdiv(m, GB_M), p.ks), dim3(G_THREADS), smem, st, dim3(1, 1, p.ks),
-                    tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols, a_box_rows(m), kil);
+                    tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols, a_box_rows(m));
 }
 
 template <int BN>
