@@ -455,9 +455,12 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             const uint32_t bn = bns[bi], ks = kss[ki];
             // One MMA occupies the tensor core ~150 cycles whatever its N, so a CTA's main loop costs
             // ~0.3 us per K block; a cluster exchange costs ~1.5 us. Split long K chains (K > 1024), and
-            // short ones only when the unsplit grid would cover less than half of the SMs.
+            // short ones four ways only when the unsplit grid would cover less than half of the SMs.
+            // Other short chains are halved at most (two accumulators still leave 256-column tiles to
+            // the large-m plan) and only with tiles of 32 columns or more per exchange.
             const bool short_k_ok = cdiv(n, 16) * 2 <= 148;
-            if (ks > 1 && (!allow_split || (num_kb <= 16 && !short_k_ok) || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
+            if (ks > 1 && num_kb <= 16 && !short_k_ok && (ks > 2 || bn < 32)) continue;
+            if (ks > 1 && (!allow_split || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
             const uint32_t per = cdiv(num_kb, ks);
             if (ks > 1 && (ks - 1) * per >= num_kb) continue;  // every CTA of the cluster gets work
             const uint32_t ctas = cdiv(n, bn) * ks;
