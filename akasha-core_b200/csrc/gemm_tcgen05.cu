@@ -406,12 +406,29 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         // same K partition as the skinny plan of this (n, k)
         const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
         if (sk.ks > 1) {
+            const uint32_t mt = cdiv(m, GB_M);
+            if (mt <= 4) {
+                // A prompt or two joining a decode batch: the K chain per CTA, not the flop count, sets the
+                // time (one MMA costs ~150 cycles whatever its width), so keep the cluster split of the
+                // decode plan, with the widest tile that still fits one wave of two CTAs per SM.
+                p.ks = sk.ks;
+                p.bn = 16;
+                const uint32_t cands[3] = {64, 32, 16};
+                for (int i = 0; i < 3; i++)
+                    if ((cands[i] / p.ks) % 4 == 0 && (uint64_t)mt * cdiv(n, cands[i]) * p.ks <= 296) { p.bn = cands[i]; break; }
+                if ((p.bn / p.ks) % 4 != 0) p.bn = 4 * p.ks;  // 16 or 32: always a legal tile width
+                const uint32_t per = cdiv(num_kb, p.ks);
+                uint32_t st = (SMEM_TWO_PER_SM - 1024 - GB_M * p.bn * 4) / stage_bytes(p.bn);
+                if (st > G_MAX_STAGES) st = G_MAX_STAGES;
+                if (st < 2) st = 2;
+                p.stages = st < per ? st : (per ? per : 1);
+                return p;
+            }
             p.kseg = sk.ks;
             p.ks = 1;
             // widest tile whose accumulators fit TMEM (kseg * bn <= 512 columns); narrower while
-            // the grid would leave most SMs idle (a prompt or two joining a decode batch)
+            // the grid would leave most SMs idle
             p.bn = 512 / sk.ks > 256 ? 256 : 512 / sk.ks;
-            const uint32_t mt = cdiv(m, GB_M);
             while (p.bn > 32 && (uint64_t)mt * cdiv(n, p.bn) < 148) p.bn /= 2;
             uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
             if (st > G_MAX_STAGES) st = G_MAX_STAGES;
