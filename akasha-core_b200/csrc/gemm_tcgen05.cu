@@ -148,7 +148,19 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
 #pragma unroll
         for (int j = 0; j < W; j++) t[j] = (EPI == AK_EPI_SILU_BF16) ? v[j] / (1.0f + __expf(-v[j])) : v[j];
         const bool vec = (gcol + W <= n) && ((ep.ldc & 3u) == 0);
-        if (vec) {
+        if (W % 8 == 0 && vec && (ep.ldc & 7u) == 0 && (gcol & 7u) == 0) {
+            // 16-byte stores: half as many L2 write requests per 32-byte sector as 8-byte ones
+#pragma unroll
+            for (int j = 0; j < W; j += 8) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    bf162 a = __floats2bfloat162_rn(t[j + 2 * e], t[j + 2 * e + 1]);
+                    pk[e] = *reinterpret_cast<uint32_t*>(&a);
+                }
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        } else if (vec) {
 #pragma unroll
             for (int j = 0; j < W; j += 4) {
                 bf162 a = __floats2bfloat162_rn(t[j], t[j + 1]), b = __floats2bfloat162_rn(t[j + 2], t[j + 3]);
@@ -162,6 +174,70 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
             for (int j = 0; j < W; j++)
                 if (gcol + j < n) dst[j] = __float2bfloat16_rn(t[j]);
         }
+    }
+}
+
+// The 16-column form used by the one-CTA-per-tile epilogue, called by whole warps. A thread owns one
+// row; its 16 columns are 64 bytes of f32 (two 32-byte sectors) or 32 bytes of bf16 (one sector).
+// Writing them with 16-byte stores costs L2 two write requests per sector, and large-m launches are
+// bound by exactly that. So adjacent lanes (rows r, r^1) trade halves: in one instruction the even
+// lane covers the first 16 bytes of a sector and the odd lane the second, first for the even row,
+// then for the odd row. Same number of instructions, every request a full sector.
+template <int EPI>
+__device__ __forceinline__ void epi_store16(const GemmEpi& ep, uint32_t row, bool row_ok, uint32_t gcol, const float* v, uint32_t n,
+                                            uint32_t lane) {
+    constexpr bool is_f32 = (EPI == AK_EPI_STORE_F32 || EPI == AK_EPI_ADD_F32 || EPI == EPI_STORE_F32_ARGMAX);
+    const bool fast = (gcol + 16 <= n) && ((gcol & 7u) == 0) && ((ep.ldc & 7u) == 0) && ep.c != nullptr;  // warp-uniform
+    if (!fast) {
+        if (row_ok && ep.c != nullptr) epi_store<EPI, 16>(ep, row, gcol, v, n);
+        return;
+    }
+    const bool odd = lane & 1u;
+    const bool partner_ok = __shfl_xor_sync(0xffffffffu, row_ok ? 1 : 0, 1) != 0;
+    const bool ok_a = odd ? partner_ok : row_ok, ok_b = odd ? row_ok : partner_ok;  // even row / odd row of the pair
+    const uint32_t ra = row & ~1u;
+    if (is_f32) {
+        float* base_a = reinterpret_cast<float*>(ep.c) + (size_t)ra * ep.ldc + gcol + (odd ? 4 : 0);
+        float* base_b = base_a + ep.ldc;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            float own[4], got[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                own[e] = odd ? v[8 * i + 4 + e] : v[8 * i + e];
+                const float send = odd ? v[8 * i + e] : v[8 * i + 4 + e];
+                got[e] = __shfl_xor_sync(0xffffffffu, send, 1);
+            }
+            float4 xa = odd ? make_float4(got[0], got[1], got[2], got[3]) : make_float4(own[0], own[1], own[2], own[3]);
+            float4 xb = odd ? make_float4(own[0], own[1], own[2], own[3]) : make_float4(got[0], got[1], got[2], got[3]);
+            if (EPI == AK_EPI_ADD_F32) {
+                float4 pa = make_float4(0.f, 0.f, 0.f, 0.f), pb = pa;
+                if (ok_a) pa = *reinterpret_cast<const float4*>(base_a + 8 * i);
+                if (ok_b) pb = *reinterpret_cast<const float4*>(base_b + 8 * i);
+                xa.x += pa.x; xa.y += pa.y; xa.z += pa.z; xa.w += pa.w;
+                xb.x += pb.x; xb.y += pb.y; xb.z += pb.z; xb.w += pb.w;
+            }
+            if (ok_a) *reinterpret_cast<float4*>(base_a + 8 * i) = xa;
+            if (ok_b) *reinterpret_cast<float4*>(base_b + 8 * i) = xb;
+        }
+    } else {
+        uint32_t pk[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) {
+            const float t0 = (EPI == AK_EPI_SILU_BF16) ? v[2 * e] / (1.0f + __expf(-v[2 * e])) : v[2 * e];
+            const float t1 = (EPI == AK_EPI_SILU_BF16) ? v[2 * e + 1] / (1.0f + __expf(-v[2 * e + 1])) : v[2 * e + 1];
+            bf162 a = __floats2bfloat162_rn(t0, t1);
+            pk[e] = *reinterpret_cast<uint32_t*>(&a);
+        }
+        uint32_t got[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) got[e] = __shfl_xor_sync(0xffffffffu, odd ? pk[e] : pk[4 + e], 1);
+        bf16* base_a = reinterpret_cast<bf16*>(ep.c) + (size_t)ra * ep.ldc + gcol + (odd ? 8 : 0);
+        bf16* base_b = base_a + ep.ldc;
+        const uint4 own = odd ? make_uint4(pk[4], pk[5], pk[6], pk[7]) : make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        const uint4 oth = make_uint4(got[0], got[1], got[2], got[3]);
+        if (ok_a) *reinterpret_cast<uint4*>(base_a) = odd ? oth : own;
+        if (ok_b) *reinterpret_cast<uint4*>(base_b) = odd ? own : oth;
     }
 }
 
@@ -286,6 +362,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         pdl_wait();  // the epilogue reads and writes C: never before the preceding kernels are done
         got = mbar_wait(&acc_bar, 0);
         if (!got && lane == 0) atomicExch(&fail_flag, 3u);
+        got = __all_sync(0xffffffffu, got);  // warp-uniform: TMEM loads and the paired stores below are warp-collective
         tc_fence_after();
     }
 
@@ -312,8 +389,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = 0.0f;
                 }
+                if (EPI != EPI_ARGMAX) epi_store16<EPI>(ep, row, row < m, n0 + c0, v, n, lane);
                 if (row < m) {
-                    if (EPI != EPI_ARGMAX) epi_store<EPI, 16>(ep, row, n0 + c0, v, n);
                     if (EPI == EPI_ARGMAX || EPI == EPI_STORE_F32_ARGMAX) {
 #pragma unroll
                         for (int j = 0; j < 16; j++)
@@ -444,7 +521,17 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         for (int i = 0; i < 5; i++)
             if ((uint64_t)mt * cdiv(n, cands[i]) >= 148) { p.bn = cands[i]; break; }
         p.ks = 1;
-        uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
+        // Two CTAs per SM (one's epilogue under the other's main loop) beat one CTA with a deeper ring.
+        uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
+        if (const char* e = getenv("AK_GEMM_BIGPLAN")) {  // tuning aid: "bn,stages" for the large-m plan
+            unsigned b = 0, t = 0;
+            if (sscanf(e, "%u,%u", &b, &t) == 2 && (b == 256 || b == 128 || b == 64 || b == 32) && t >= 1) {
+                p.bn = b;
+                st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
+                if (t < st) st = t;
+                if (st < 1) st = 1;
+            }
+        }
         if (st > G_MAX_STAGES) st = G_MAX_STAGES;
         if (p.bn <= 64 && st > 6) st = 6;
         p.stages = st < num_kb ? st : (num_kb ? num_kb : 1);
