@@ -125,6 +125,12 @@ class Runner {
     void* qbuf_ = nullptr;
     void* attn_ = nullptr;
     void* up_ = nullptr;
+    // bf16, single GPU: the per-layer RMSNorms are folded into the projections that follow them. hb_ is
+    // a bf16 copy of the residual stream (written by the embedding and by the out-proj / ffn-down
+    // epilogues); qkv_f_/up_f_ are the qkv / ffn-up weights with the norm gain multiplied in.
+    bool fuse_norm_ = false;
+    void* hb_ = nullptr;
+    std::vector<void*> qkv_f_, up_f_;
     void* xf_ = nullptr;
     float* logits_ = nullptr;
     uint32_t logits_ld_ = 0;          // row pitch of logits_ (padded to 4 in bf16 mode)

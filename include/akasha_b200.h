@@ -240,6 +240,17 @@ typedef enum ak_gemm_epilogue {
     AK_EPI_SILU_BF16 = 3   /* C bf16 = silu(acc)              (matmul + silu)     */
 } ak_gemm_epilogue;
 AK_API int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue);
+
+/* ak_gemm_bf16 with two fusions the engine uses in bf16 mode (no reference counterpart: they replace
+ * the separate RMSNORM nodes of the layer graphs, src/nn/inference_graphs.rs:222-236, 300-314):
+ *   c_bf16_copy  (AK_EPI_ADD_F32 only, may be NULL): bf16 [m, n] copy of the updated C rows, i.e. the
+ *                residual stream as the next projection's activation;
+ *   rmsnorm_rows != 0: every output row i is scaled by 1/sqrt(mean_k(A[i,k]^2) + eps) before the
+ *                epilogue op, the mean taken over the bf16 activation row the tensor core consumed.
+ *                With the norm's gain multiplied into Wt (Wt[n,k] * gain[k]) this is
+ *                rmsnorm(A) @ W without a normalisation kernel and without the normalised copy. */
+AK_API int ak_gemm_bf16_ex(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue,
+                           void* c_bf16_copy, uint32_t rmsnorm_rows, float eps);
 /* Make the [n,k] bf16 operand from a reference-layout f32 [k,n] matrix (device to device). */
 AK_API int ak_transpose_to_bf16(void* stream, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);
 AK_API int ak_f32_to_bf16(void* stream, const float* src, void* dst, uint64_t n);
