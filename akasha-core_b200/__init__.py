@@ -65,7 +65,7 @@ FlashAttnMeta = _u32struct("FlashAttnMeta", ["seq_len", "dim", "head_dim", "scal
 AttnDecodeParams = _u32struct("AttnDecodeParams", ["rows", "heads", "head_dim", "block_size", "max_blocks_per_seq",
                                                    "scale", "kv_dtype", "n_splits", "pool_blocks"], floats=("scale",))
 EngineConfig = _u32struct("EngineConfig", ["max_seqs", "max_seq_len", "kv_blocks", "block_size", "max_batch_tokens",
-                                           "use_cuda_graph", "stop_on_eos", "attn_timing"])
+                                           "use_cuda_graph", "stop_on_eos", "attn_timing", "async_steps"])
 
 
 class EngineStats(C.Structure):
@@ -115,7 +115,6 @@ _PROTOS = {
     "ak_rope_kv_append": [vp, vp, vp, vp, vp, vp, vp] + [C.c_uint32] * 5,
     "ak_rmsnorm_rope_residual": [vp, vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32, C.c_uint32],
     "ak_gemm_bf16": [vp, vp, vp, vp, MatMulMeta, C.c_uint32],
-    "ak_gemm_bf16_ex": [vp, vp, vp, vp, MatMulMeta, C.c_uint32, vp, C.c_uint32, C.c_float],
     "ak_transpose_to_bf16": [vp, vp, vp, C.c_uint32, C.c_uint32],
     "ak_f32_to_bf16": [vp, vp, vp, C.c_uint64],
     "ak_bf16_to_f32": [vp, vp, vp, C.c_uint64],
@@ -145,6 +144,7 @@ _PROTOS = {
     "ak_engine_destroy": [vp],
     "ak_engine_submit": [vp, u32p, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64)],
     "ak_engine_step": [vp, u32p, u32p],
+    "ak_engine_run": [vp, C.c_uint64, C.POINTER(C.c_uint64)],
     "ak_engine_poll": [vp, C.c_uint64, u32p, C.c_uint32, u32p, C.POINTER(C.c_int)],
     "ak_engine_block_table": [vp, C.c_uint64, i32p, C.c_uint32, u32p],
     "ak_engine_clear_finished": [vp],
@@ -478,10 +478,10 @@ class Engine:
 
     def __init__(self, ctx: Context, weights: ModelWeights, max_seqs: int, max_seq_len: int, kv_blocks: int = 0,
                  max_batch_tokens: int = 0, use_cuda_graph: bool = True, stop_on_eos: bool = False,
-                 attn_timing: bool = False):
+                 attn_timing: bool = False, async_steps: bool = False):
         self.ctx, self.weights = ctx, weights
         cfg = EngineConfig(max_seqs, max_seq_len, kv_blocks, 16, max_batch_tokens, int(use_cuda_graph),
-                           int(stop_on_eos), int(attn_timing))
+                           int(stop_on_eos), int(attn_timing), int(async_steps))
         self.h = vp()
         check(lib().ak_engine_create(ctx.h, weights.h, C.byref(cfg), C.byref(self.h)))
 
@@ -497,13 +497,10 @@ class Engine:
         return r.value, w.value
 
     def run_to_completion(self, max_steps: int = 1 << 30) -> int:
-        steps = 0
-        while steps < max_steps:
-            r, w = self.step()
-            steps += 1
-            if r == 0 and w == 0:
-                break
-        return steps
+        """Step until nothing is running or waiting (the loop runs inside the library)."""
+        n = C.c_uint64(0)
+        check(lib().ak_engine_run(self.h, max_steps, C.byref(n)))
+        return n.value
 
     def poll(self, seq_id: int, cap: int = 8192):
         out = np.zeros(cap, np.uint32)

@@ -29,7 +29,7 @@ __global__ void embedding_kernel(const uint32_t* __restrict__ tokens, const floa
 template <typename WT>
 __global__ void embed_rows_kernel(const int32_t* __restrict__ tok_src, uint32_t idx_stride,
                                   const uint32_t* __restrict__ sampled, const WT* __restrict__ table,
-                                  float* __restrict__ hidden, bf16* __restrict__ hidden_bf16, uint32_t vocab, uint32_t dim) {
+                                  float* __restrict__ hidden, uint32_t vocab, uint32_t dim) {
     pdl_wait();
     pdl_trigger();
     uint32_t r = blockIdx.x;
@@ -41,21 +41,17 @@ __global__ void embed_rows_kernel(const int32_t* __restrict__ tok_src, uint32_t 
     bool ok = active && id < vocab;
     const WT* src = table + (size_t)(ok ? id : 0) * dim;
     float* dst = hidden + (size_t)r * dim;
-    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) {
-        const float v = ok ? Cvt<WT>::to_f(src[i]) : 0.0f;
-        dst[i] = v;
-        if (hidden_bf16) hidden_bf16[(size_t)r * dim + i] = __float2bfloat16_rn(v);
-    }
+    for (uint32_t i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? Cvt<WT>::to_f(src[i]) : 0.0f;
 }
 
 int launch_embed_rows(cudaStream_t st, const int32_t* tok_src, uint32_t idx_stride, const uint32_t* sampled,
                       const void* table, uint32_t table_dtype, float* hidden, uint32_t vocab, uint32_t dim,
-                      uint32_t rows, void* hidden_bf16) {
+                      uint32_t rows) {
     if (rows == 0) return AK_OK;
     if (table_dtype == AK_F32)
-        AK_TRY(launch_k(embed_rows_kernel<float>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const float*)table, hidden, (bf16*)hidden_bf16, vocab, dim));
+        AK_TRY(launch_k(embed_rows_kernel<float>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const float*)table, hidden, vocab, dim));
     else
-        AK_TRY(launch_k(embed_rows_kernel<bf16>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const bf16*)table, hidden, (bf16*)hidden_bf16, vocab, dim));
+        AK_TRY(launch_k(embed_rows_kernel<bf16>, dim3(rows), dim3(256), 0, st, NO_CLUSTER, tok_src, idx_stride, sampled, (const bf16*)table, hidden, vocab, dim));
     return AK_OK;
 }
 
@@ -391,22 +387,6 @@ int launch_rope_kv_append(cudaStream_t st, const float* qkv, const int32_t* posi
             qkv, positions, slots, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, rope_table, rope_table_len, tokens,
             heads, head_dim, block_size, idx_stride));
     }
-    return AK_OK;
-}
-
-// ============================================================================ norm gain folded into a projection
-__global__ void fold_gain_bf16_kernel(const bf16* __restrict__ w, const float* __restrict__ gain, bf16* __restrict__ out,
-                                      size_t total, uint32_t k) {
-    pdl_wait();
-    pdl_trigger();
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < total) out[i] = __float2bfloat16_rn(__bfloat162float(w[i]) * gain[i % k]);
-}
-int launch_fold_gain_bf16(cudaStream_t st, const void* w_nk, const float* gain, void* out_nk, uint32_t n, uint32_t k) {
-    const size_t total = (size_t)n * k;
-    if (total == 0) return AK_OK;
-    AK_TRY(launch_k(fold_gain_bf16_kernel, dim3((unsigned)cdiv64(total, 256)), dim3(256), 0, st, NO_CLUSTER, (const bf16*)w_nk, gain,
-                    (bf16*)out_nk, total, k));
     return AK_OK;
 }
 

@@ -44,7 +44,49 @@ struct ak_engine {
     uint64_t next_id = 1;
     ak_engine_stats stats{};
     unsigned long long launch_base = 0;
+    // a step that has been launched and whose tokens have not been read yet
+    struct Pending {
+        bool active = false;
+        uint32_t bank = 0;
+        std::vector<std::pair<Seq*, uint32_t>> fill;  // (sequence, index into its `generated`), slot = seq->slot at launch
+        std::vector<uint32_t> fill_slot;
+        bool any_decode = false;
+        uint64_t attn_bytes = 0;
+    } pending;
+    uint64_t step_index = 0;
+    bool async_ok() const { return cfg.async_steps != 0 && cfg.stop_on_eos == 0; }
 };
+
+// Wait for the step in flight and write its tokens into their sequences.
+static int collect(ak_engine* e) {
+    ak_engine::Pending& p = e->pending;
+    if (!p.active) return AK_OK;
+    Runner& r = e->runner;
+    int rc = r.wait_bank(p.bank);
+    if (rc) return rc;
+    const uint32_t cur = r.bank();
+    r.set_bank(p.bank);
+    const uint32_t* sampled = r.h_sampled();
+    const ak_model_config& mc = e->w->cfg;
+    for (size_t i = 0; i < p.fill.size(); i++) {
+        Seq* s = p.fill[i].first;
+        const uint32_t tok = sampled[p.fill_slot[i]];
+        s->generated[p.fill[i].second] = tok;
+        if (e->cfg.stop_on_eos && tok == mc.eos_token) s->finished = true;
+    }
+    if (e->cfg.attn_timing) e->stats.step_gpu_ms_total += r.last_step_gpu_ms();
+    if (e->cfg.attn_timing && p.any_decode) {
+        float ms = r.last_attn_ms();
+        if (ms > 0.0f) {
+            e->stats.attn_ms_total += ms;
+            e->stats.attn_launches_timed++;
+            e->stats.attn_bytes_total += p.attn_bytes;
+        }
+    }
+    r.set_bank(cur);
+    p.active = false;
+    return AK_OK;
+}
 
 static void release(ak_engine* e, Seq* s) {
     for (int32_t b : s->blocks) e->free_blocks.insert(b);
@@ -88,6 +130,7 @@ int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak
 
 int ak_engine_destroy(ak_engine* e) {
     if (!e) return AK_OK;
+    collect(e);
     for (auto& kv : e->all) delete kv.second;
     delete e;
     return AK_OK;
@@ -117,6 +160,11 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     const uint32_t S = e->cfg.max_seqs;
     const ak_model_config& mc = e->w->cfg;
     const unsigned long long launches0 = g_launch_count;
+    // Without async steps the previous step's tokens decide who has finished: read them first.
+    // With async steps sequence ends depend on lengths only, so this step is planned and launched
+    // while the previous one still runs, and the previous one's tokens are read afterwards.
+    if (!e->async_ok()) { int rc0 = collect(e); if (rc0) return rc0; }
+    r.set_bank(e->async_ok() ? (uint32_t)(e->step_index & 1u) : 0u);
 
     // 1. retire sequences that finished in the previous step (their blocks go back first)
     for (uint32_t i = 0; i < S; i++)
@@ -142,8 +190,6 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
             s->blocks.push_back(*it);
             e->free_blocks.erase(it);
         }
-        int32_t* bt = r.h_block_table(slot);
-        for (uint32_t b = 0; b < r.max_blocks(); b++) bt[b] = b < need ? s->blocks[b] : 0;
         pf_rows += (uint32_t)s->prompt.size();
         admitted.push_back(s);
     }
@@ -161,6 +207,12 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         Seq* s = e->slots[i];
         bool is_new = false;
         for (Seq* a : admitted) is_new |= (a == s);
+        if (s && !s->finished) {
+            // every bank of the descriptor carries its own copy of the tables: refresh the live ones
+            int32_t* bt = r.h_block_table(i);
+            const uint32_t nb = (uint32_t)s->blocks.size();
+            for (uint32_t b = 0; b < r.max_blocks(); b++) bt[b] = b < nb ? s->blocks[b] : 0;
+        }
         if (s && !is_new && !s->finished) {
             const uint32_t pos = s->cached;
             rows[i] = {-(int32_t)(i + 1), (int32_t)pos, s->blocks[pos / 16] * 16 + (int32_t)(pos % 16), (int32_t)i};
@@ -195,6 +247,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         if (P > max_pf) max_pf = P;
     }
     if (!any_decode && admitted.empty()) {
+        int rcf = collect(e);  // nothing to launch: make the last step's tokens visible
+        if (rcf) return rcf;
         if (n_running) *n_running = 0;
         if (n_waiting) *n_waiting = (uint32_t)e->waiting.size();
         return AK_OK;
@@ -206,11 +260,15 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     if (graph) rc = r.run_graph(pf_rows, (uint32_t)admitted.size(), max_pf);
     else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
     if (rc) return rc;
-    rc = r.sync();
+    rc = r.mark_done();
     if (rc) return rc;
 
-    // 5. collect this step's tokens
-    const uint32_t* sampled = r.h_sampled();
+    // 5. advance the sequences by one token (the value is filled in when the step is collected)
+    ak_engine::Pending now;
+    now.active = true;
+    now.bank = r.bank();
+    now.any_decode = any_decode;
+    now.attn_bytes = attn_bytes;
     uint32_t running = 0;
     for (uint32_t i = 0; i < S; i++) {
         Seq* s = e->slots[i];
@@ -218,11 +276,24 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         bool is_new = false;
         for (Seq* a : admitted) is_new |= (a == s);
         s->cached = is_new ? (uint32_t)s->prompt.size() : s->cached + 1;
-        const uint32_t tok = sampled[i];
-        s->generated.push_back(tok);
+        now.fill.emplace_back(s, (uint32_t)s->generated.size());
+        now.fill_slot.push_back(i);
+        s->generated.push_back(0);
         const uint32_t total = (uint32_t)(s->prompt.size() + s->generated.size());
-        if (total >= s->max_total || (e->cfg.stop_on_eos && tok == mc.eos_token)) s->finished = true;
+        if (total >= s->max_total) s->finished = true;
         else running++;
+    }
+    // the previous step (other bank) has had this step's host work to finish in: read its tokens now
+    rc = collect(e);
+    if (rc) return rc;
+    e->pending = std::move(now);
+    e->step_index++;
+    if (!e->async_ok()) {
+        rc = collect(e);
+        if (rc) return rc;
+        // an end-of-sequence token may have finished sequences that the length rule left running
+        running = 0;
+        for (uint32_t i = 0; i < S; i++) if (e->slots[i] && !e->slots[i]->finished) running++;
     }
     e->stats.steps++;
     e->stats.decode_tokens += n_dec;
@@ -231,23 +302,33 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     e->stats.kernel_launches += (g_launch_count - launches0);
     e->stats.h2d_bytes = r.h2d_bytes;
     e->stats.launch_host_ms_total = r.launch_host_ms;
-    if (e->cfg.attn_timing) e->stats.step_gpu_ms_total += r.last_step_gpu_ms();
     e->stats.d2h_bytes = r.d2h_bytes;
-    if (e->cfg.attn_timing && any_decode) {
-        float ms = r.last_attn_ms();
-        if (ms > 0.0f) {
-            e->stats.attn_ms_total += ms;
-            e->stats.attn_launches_timed++;
-            e->stats.attn_bytes_total += attn_bytes;
-        }
-    }
+    (void)mc;
     if (n_running) *n_running = running;
     if (n_waiting) *n_waiting = (uint32_t)e->waiting.size();
     return AK_OK;
 }
 
+int ak_engine_run(ak_engine* e, uint64_t max_steps, uint64_t* steps_done) {
+    AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_run: null engine");
+    uint64_t n = 0;
+    for (;;) {
+        if (max_steps && n >= max_steps) break;
+        uint32_t running = 0, waiting = 0;
+        int rc = ak_engine_step(e, &running, &waiting);
+        if (rc) return rc;
+        n++;
+        if (running == 0 && waiting == 0) break;
+    }
+    int rc = collect(e);
+    if (rc) return rc;
+    if (steps_done) *steps_done = n;
+    return AK_OK;
+}
+
 int ak_engine_poll(ak_engine* e, uint64_t seq_id, uint32_t* out, uint32_t cap, uint32_t* n_out, int* finished) {
     AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_poll: null engine");
+    { int rcf = collect(e); if (rcf) return rcf; }
     auto it = e->all.find(seq_id);
     AK_REQUIRE(it != e->all.end(), AK_ERR_NOT_FOUND, "ak_engine_poll: unknown sequence %llu", (unsigned long long)seq_id);
     Seq* s = it->second;
@@ -261,6 +342,7 @@ int ak_engine_poll(ak_engine* e, uint64_t seq_id, uint32_t* out, uint32_t cap, u
 
 int ak_engine_block_table(ak_engine* e, uint64_t seq_id, int32_t* out, uint32_t cap, uint32_t* n_out) {
     AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_block_table: null engine");
+    { int rcf = collect(e); if (rcf) return rcf; }
     auto it = e->all.find(seq_id);
     AK_REQUIRE(it != e->all.end(), AK_ERR_NOT_FOUND, "ak_engine_block_table: unknown sequence %llu", (unsigned long long)seq_id);
     Seq* s = it->second;
@@ -273,6 +355,7 @@ int ak_engine_block_table(ak_engine* e, uint64_t seq_id, int32_t* out, uint32_t 
 
 int ak_engine_clear_finished(ak_engine* e) {
     AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_clear_finished: null engine");
+    { int rcf = collect(e); if (rcf) return rcf; }
     for (auto it = e->all.begin(); it != e->all.end();) {
         Seq* s = it->second;
         if (s->finished) {
@@ -288,6 +371,7 @@ int ak_engine_clear_finished(ak_engine* e) {
 
 int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out) {
     AK_REQUIRE(e && out, AK_ERR_INVALID_ARG, "ak_engine_get_stats: null pointer");
+    { int rcf = collect(e); if (rcf) return rcf; }
     *out = e->stats;
     return AK_OK;
 }

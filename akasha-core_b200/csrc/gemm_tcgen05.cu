@@ -113,9 +113,6 @@ struct GemmEpi {
     float* amax_val;    // [m][amax_ld] per-tile row maxima (argmax epilogues)
     uint32_t* amax_idx; // [m][amax_ld] their column indices
     uint32_t amax_ld;
-    bf16* c2;           // ADD_F32 only: a bf16 copy of the updated rows [m, ldc] (the next GEMM's activation), may be null
-    uint32_t norm;      // 1: scale every output row by 1/sqrt(mean(a_row^2) + eps), a_row = the bf16 activation row the
-    float eps;          //    MMA consumed (RMSNorm folded into the projection; the gain lives in the weight)
 };
 
 enum { EPI_ARGMAX = 4, EPI_STORE_F32_ARGMAX = 5 };
@@ -135,13 +132,6 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
                     o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
                 }
                 *reinterpret_cast<float4*>(dst + j) = o;
-                if (EPI == AK_EPI_ADD_F32 && ep.c2) {
-                    bf162 a = __floats2bfloat162_rn(o.x, o.y), b = __floats2bfloat162_rn(o.z, o.w);
-                    uint2 pk;
-                    pk.x = *reinterpret_cast<uint32_t*>(&a);
-                    pk.y = *reinterpret_cast<uint32_t*>(&b);
-                    *reinterpret_cast<uint2*>(ep.c2 + (size_t)row * ep.ldc + gcol + j) = pk;
-                }
             }
         } else {
 #pragma unroll
@@ -150,7 +140,6 @@ __device__ __forceinline__ void epi_store(const GemmEpi& ep, uint32_t row, uint3
                     float o = v[j];
                     if (EPI == AK_EPI_ADD_F32) o += dst[j];
                     dst[j] = o;
-                    if (EPI == AK_EPI_ADD_F32 && ep.c2) ep.c2[(size_t)row * ep.ldc + gcol + j] = __float2bfloat16_rn(o);
                 }
         }
     } else if (EPI == AK_EPI_STORE_BF16 || EPI == AK_EPI_SILU_BF16) {
@@ -230,13 +219,6 @@ __device__ __forceinline__ void epi_store16(const GemmEpi& ep, uint32_t row, boo
             }
             if (ok_a) *reinterpret_cast<float4*>(base_a + 8 * i) = xa;
             if (ok_b) *reinterpret_cast<float4*>(base_b + 8 * i) = xb;
-            if (EPI == AK_EPI_ADD_F32 && ep.c2) {
-                bf16* c2a = ep.c2 + (size_t)ra * ep.ldc + gcol + (odd ? 4 : 0) + 8 * i;
-                bf162 a0 = __floats2bfloat162_rn(xa.x, xa.y), a1 = __floats2bfloat162_rn(xa.z, xa.w);
-                bf162 b0 = __floats2bfloat162_rn(xb.x, xb.y), b1 = __floats2bfloat162_rn(xb.z, xb.w);
-                if (ok_a) *reinterpret_cast<uint2*>(c2a) = make_uint2(*reinterpret_cast<uint32_t*>(&a0), *reinterpret_cast<uint32_t*>(&a1));
-                if (ok_b) *reinterpret_cast<uint2*>(c2a + ep.ldc) = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
-            }
         }
     } else {
         uint32_t pk[8];
@@ -279,7 +261,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __shared__ uint64_t full_bar[G_MAX_STAGES], empty_bar[G_MAX_STAGES], acc_bar;
     __shared__ uint32_t tmem_base_sm;
     __shared__ uint32_t fail_flag;
-    __shared__ float ssq_x[8][GB_M];  // fused norm, split K: every CTA's partial sum of squares per row
 
     cg::cluster_group cluster = cg::this_cluster();
     const uint32_t ks = cluster.num_blocks();
@@ -295,8 +276,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t num_kb = (kb_begin + per <= num_kb_total) ? per : num_kb_total - kb_begin;
 
     if (threadIdx.x == 0) {
-        // a stage is free once its MMAs have read it and, with the fused norm, once the four epilogue warps have too
-        for (uint32_t s = 0; s < stages; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], ep.norm ? 5 : 1); }
+        for (uint32_t s = 0; s < stages; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
         fail_flag = 0;
         mbar_fence_init();
@@ -378,38 +358,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t trow = quad * 32 + lane;  // row inside the tile
     const uint32_t row = m0 + trow;
     bool got = true;
-    // Fused RMSNorm: while the main loop runs, each epilogue thread sums the squares of ITS activation
-    // row from the staged tiles (the bf16 values the MMA multiplies), one partial per K segment so
-    // that the total is formed in the same order whether the segments live in one CTA or in a cluster.
-    float ssq[8];
-#pragma unroll
-    for (int q = 0; q < 8; q++) ssq[q] = 0.0f;
-    if (warp >= 2 && ep.norm) {
-        const uint32_t per_seg = (num_kb + kseg - 1) / kseg;
-        for (uint32_t i = 0; i < num_kb; i++) {
-            const uint32_t s = i % stages, ph = (i / stages) & 1u, seg = i / per_seg;
-            bool ok = mbar_wait(&full_bar[s], ph);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { if (lane == 0) atomicExch(&fail_flag, 4u); break; }
-            const uint8_t* a_row = smem + (size_t)s * C::STAGE_BYTES + trow * 128u;
-            float part = 0.0f;
-#pragma unroll
-            for (uint32_t c = 0; c < 8; c++) {
-                const uint4 q4 = *reinterpret_cast<const uint4*>(a_row + ((c ^ (trow & 7u)) << 4));
-                const uint32_t w4[4] = {q4.x, q4.y, q4.z, q4.w};
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float lo = __uint_as_float(w4[e] << 16), hi = __uint_as_float(w4[e] & 0xffff0000u);
-                    part = fmaf(lo, lo, part);
-                    part = fmaf(hi, hi, part);
-                }
-            }
-#pragma unroll
-            for (int q = 0; q < 8; q++) if ((uint32_t)q == seg) ssq[q] += part;
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[s]);
-        }
-    }
     if (warp >= 2) {
         pdl_wait();  // the epilogue reads and writes C: never before the preceding kernels are done
         got = mbar_wait(&acc_bar, 0);
@@ -422,13 +370,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (warp >= 2 && got) {
             float best = -INFINITY;
             uint32_t best_i = 0xffffffffu;
-            float rstd = 1.0f;
-            if (ep.norm) {
-                float tot = ssq[0];
-#pragma unroll
-                for (int q = 1; q < 8; q++) if ((uint32_t)q < kseg) tot += ssq[q];  // segment order = cluster rank order
-                rstd = 1.0f / sqrtf(tot / (float)k + ep.eps);
-            }
 #pragma unroll 1
             for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 16) {
                 uint32_t r[16];
@@ -447,10 +388,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j++) v[j] = 0.0f;
-                }
-                if (ep.norm) {
-#pragma unroll
-                    for (int j = 0; j < 16; j++) v[j] *= rstd;
                 }
                 if (EPI != EPI_ARGMAX) epi_store16<EPI>(ep, row, row < m, n0 + c0, v, n, lane);
                 if (row < m) {
@@ -491,17 +428,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 }
             }
         }
-        if (ep.norm && warp >= 2)
-            for (uint32_t d = 0; d < ks; d++) cluster.map_shared_rank(&ssq_x[0][0], d)[rank * GB_M + trow] = ssq[0];
         tc_fence_before();
         cluster_sync_all();  // every partial slice has landed in its owner's shared memory
         if (warp >= 2 && got && row < m) {
-            float rstd = 1.0f;
-            if (ep.norm) {
-                float tot = 0.0f;
-                for (uint32_t src = 0; src < ks; src++) tot += ssq_x[src][trow];  // rank order
-                rstd = 1.0f / sqrtf(tot / (float)k + ep.eps);
-            }
 #pragma unroll 1
             for (uint32_t j = 0; j < SL; j += 4) {
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -509,7 +438,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     float4 p = *reinterpret_cast<const float4*>(red + ((size_t)src * GB_M + trow) * SL + j);
                     acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
                 }
-                float v[4] = {acc.x * rstd, acc.y * rstd, acc.z * rstd, acc.w * rstd};
+                float v[4] = {acc.x, acc.y, acc.z, acc.w};
                 epi_store<EPI, 4>(ep, row, n0 + rank * SL + j, v, n);
             }
         }
@@ -720,25 +649,14 @@ static int check_operands(const void* a, const void* wt, uint32_t k) {
 
 int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k,
                      uint32_t epilogue, uint32_t ldc, bool invariant) {
-    return launch_gemm_bf16_ex(st, a, wt, c, m, n, k, epilogue, ldc, invariant, nullptr, false, 0.0f);
-}
-
-// c2 (ADD_F32 only): bf16 copy of the updated rows. norm: scale each output row by the RMSNorm factor of
-// its activation row (computed from the staged bf16 tiles; the norm's gain is expected in the weight).
-int launch_gemm_bf16_ex(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k,
-                        uint32_t epilogue, uint32_t ldc, bool invariant, void* c2, bool norm, float eps) {
     if (m == 0 || n == 0) return AK_OK;
     int rc = check_operands(a, wt, k);
     if (rc) return rc;
     AK_REQUIRE(epilogue <= AK_EPI_SILU_BF16, AK_ERR_INVALID_ARG, "gemm_bf16: unknown epilogue %u", epilogue);
     AK_REQUIRE(((uintptr_t)c % 16) == 0, AK_ERR_INVALID_ARG, "gemm_bf16: output must be 16-byte aligned");
-    AK_REQUIRE(c2 == nullptr || epilogue == AK_EPI_ADD_F32, AK_ERR_INVALID_ARG, "gemm_bf16: the bf16 copy goes with the += epilogue");
     GemmEpi ep{};
     ep.c = c;
     ep.ldc = ldc ? ldc : n;
-    ep.c2 = (bf16*)c2;
-    ep.norm = norm ? 1u : 0u;
-    ep.eps = eps;
     // the split-K exchange stores 4-column groups: it needs 4-aligned rows
     const bool allow_split = (ep.ldc % 4) == 0;
     return launch_planned(st, a, wt, ep, m, n, k, epilogue, plan_gemm(m, n, k, allow_split, invariant));
@@ -774,12 +692,6 @@ int gemm_bf16_check_status(cudaStream_t st) {
 }  // namespace ak
 
 using namespace ak;
-extern "C" int ak_gemm_bf16_ex(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue,
-                               void* c_bf16_copy, uint32_t rmsnorm_rows, float eps) {
-    AK_REQUIRE(a && wt && c, AK_ERR_INVALID_ARG, "ak_gemm_bf16_ex: null pointer");
-    return launch_gemm_bf16_ex(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, m.n, false, c_bf16_copy, rmsnorm_rows != 0, eps);
-}
-
 extern "C" int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue) {
     AK_REQUIRE(a && wt && c, AK_ERR_INVALID_ARG, "ak_gemm_bf16: null pointer");
     return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, m.n, false);

@@ -11,7 +11,7 @@ namespace ak {
 // idx_stride: distance (in int32) between consecutive rows' entries of tok_src / positions / slots.
 int launch_embed_rows(cudaStream_t st, const int32_t* tok_src, uint32_t idx_stride, const uint32_t* sampled,
                       const void* table, uint32_t table_dtype, float* hidden, uint32_t vocab, uint32_t dim,
-                      uint32_t rows, void* hidden_bf16 = nullptr);  // optional bf16 copy of the rows
+                      uint32_t rows);
 // y[r] = rmsnorm(x[row_map ? row_map[r] : r]) * w ; rows whose mapped index is < 0 are zeroed.
 int launch_rmsnorm(cudaStream_t st, const float* x, const float* w, void* y, uint32_t out_dtype,
                    const int32_t* row_map, uint32_t rows, uint32_t size, float eps);
@@ -58,10 +58,6 @@ int launch_gemm_f32(cudaStream_t st, const float* a, const float* b, float* c, u
 // throughput for m > 128. false = fastest plan for the given m.
 int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n,
                      uint32_t k, uint32_t epilogue, uint32_t ldc, bool invariant);
-int launch_gemm_bf16_ex(cudaStream_t st, const void* a, const void* wt, void* c, uint32_t m, uint32_t n, uint32_t k,
-                        uint32_t epilogue, uint32_t ldc, bool invariant, void* c2_bf16, bool norm, float eps);
-// out[n,k] = bf16(w[n,k] * gain[k]): an RMSNorm gain folded into the projection that follows it.
-int launch_fold_gain_bf16(cudaStream_t st, const void* w_nk, const float* gain, void* out_nk, uint32_t n, uint32_t k);
 int gemm_bf16_check_status(cudaStream_t st);  // reads the device status word (syncs the stream)
 // lm_head with the greedy argmax fused into the epilogue: every N tile writes each row's
 // (max, first index) to part_val/part_idx [m][gemm_argmax_tiles()]; launch_argmax_finish reduces

@@ -230,21 +230,23 @@ Runner::~Runner() {
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
-    if (ev_attn0_) cudaEventDestroy(ev_attn0_);
-    if (ev_attn1_) cudaEventDestroy(ev_attn1_);
-    if (ev_g0_) cudaEventDestroy(ev_g0_);
-    if (ev_g1_) cudaEventDestroy(ev_g1_);
+    for (Bank& b : banks_) {
+        if (b.ev_attn0) cudaEventDestroy(b.ev_attn0);
+        if (b.ev_attn1) cudaEventDestroy(b.ev_attn1);
+        if (b.ev_g0) cudaEventDestroy(b.ev_g0);
+        if (b.ev_g1) cudaEventDestroy(b.ev_g1);
+        if (b.ev_done) cudaEventDestroy(b.ev_done);
+    }
     for (void* p : k_pool_) cudaFree(p);
     for (void* p : v_pool_) cudaFree(p);
     cudaFree(hidden_); cudaFree(xn_); cudaFree(qkv_); cudaFree(qbuf_); cudaFree(attn_); cudaFree(up_);
-    cudaFree(hb_);
-    for (void* p : qkv_f_) cudaFree(p);
-    for (void* p : up_f_) cudaFree(p);
     cudaFree(amax_val_); cudaFree(amax_idx_); cudaFree(tp_tmp_);
     cudaFree(xf_); cudaFree(logits_); cudaFree(attn_scratch_); cudaFree(rope_table_);
     cudaFree(d_desc_); cudaFree(d_sampled_);
-    if (h_desc_) cudaFreeHost(h_desc_);
-    if (h_sampled_) cudaFreeHost(h_sampled_);
+    for (Bank& b : banks_) {
+        if (b.h_desc) cudaFreeHost(b.h_desc);
+        if (b.h_sampled) cudaFreeHost(b.h_sampled);
+    }
 }
 
 int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq_len, uint32_t kv_blocks, uint32_t max_prefill_tokens) {
@@ -273,12 +275,18 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     d_.block_tables = d_.pf_slot + max_seqs;
     d_.rows = align_up(d_.block_tables + max_seqs * max_blocks_, 4);
     d_.total = d_.rows + max_rows_ * 4;
-    AK_CUDA(cudaMallocHost((void**)&h_desc_, (size_t)d_.total * 4));
-    memset(h_desc_, 0, (size_t)d_.total * 4);
+    for (Bank& b : banks_) {
+        AK_CUDA(cudaMallocHost((void**)&b.h_desc, (size_t)d_.total * 4));
+        memset(b.h_desc, 0, (size_t)d_.total * 4);
+        AK_CUDA(cudaMallocHost((void**)&b.h_sampled, (size_t)max_seqs * 4));
+        memset(b.h_sampled, 0, (size_t)max_seqs * 4);
+    }
+    bank_ = 0;
+    h_desc_ = banks_[0].h_desc;
+    h_sampled_ = banks_[0].h_sampled;
     AK_CUDA(cudaMalloc((void**)&d_desc_, (size_t)d_.total * 4));
     AK_CUDA(cudaMemset(d_desc_, 0, (size_t)d_.total * 4));
-    AK_CUDA(cudaMallocHost((void**)&h_sampled_, (size_t)max_seqs * 4));
-    memset(h_sampled_, 0, (size_t)max_seqs * 4);
+
     AK_CUDA(cudaMalloc((void**)&d_sampled_, (size_t)max_seqs * 4));
     AK_CUDA(cudaMemset(d_sampled_, 0, (size_t)max_seqs * 4));
 
@@ -303,26 +311,6 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
         AK_CUDA(cudaMemsetAsync(tp_tmp_, 0, R * D * 4, ctx->stream));
     }
     AK_CUDA(cudaMalloc(&xf_, (size_t)max_seqs * D * act));
-    {
-        // Off unless AK_FUSE_NORM=1: it removes 24 of the 100 launches of a decode step, yet measured slower
-        // (0.73 ms against 0.69 ms per step): behind a small norm kernel the next projection's CTAs are
-        // already resident and fetch their weight tiles while it runs; behind another projection they are not.
-        const char* e = getenv("AK_FUSE_NORM");
-        fuse_norm_ = w->dtype == AK_BF16 && tp_ == 1 && (D % 64) == 0 && (e && e[0] == '1');
-    }
-    if (fuse_norm_) {
-        AK_CUDA(cudaMalloc(&hb_, R * D * 2));
-        AK_CUDA(cudaMemsetAsync(hb_, 0, R * D * 2, ctx->stream));
-        for (uint32_t l = 0; l < c.num_layers; l++) {
-            void *q = nullptr, *u = nullptr;
-            AK_CUDA(cudaMalloc(&q, (size_t)3 * dq_ * D * 2));
-            AK_CUDA(cudaMalloc(&u, (size_t)ffn_l_ * D * 2));
-            qkv_f_.push_back(q);
-            up_f_.push_back(u);
-            AK_TRY(launch_fold_gain_bf16(ctx->stream, w->blocks[l].qkv, w->blocks[l].norm_1, q, 3 * dq_, D));
-            AK_TRY(launch_fold_gain_bf16(ctx->stream, w->blocks[l].up, w->blocks[l].norm_2, u, ffn_l_, D));
-        }
-    }
     logits_ld_ = (w->dtype == AK_BF16) ? (V + 3) / 4 * 4 : V;
     AK_CUDA(cudaMalloc((void**)&logits_, (size_t)max_seqs * logits_ld_ * 4));
     if (w->dtype == AK_BF16) {
@@ -352,10 +340,14 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
         }
     AK_CUDA(cudaMalloc((void**)&rope_table_, tab.size() * sizeof(float2)));
     AK_CUDA(cudaMemcpyAsync(rope_table_, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, ctx->stream));
-    AK_CUDA(cudaEventCreate(&ev_attn0_));
-    AK_CUDA(cudaEventCreate(&ev_attn1_));
-    AK_CUDA(cudaEventCreate(&ev_g0_));
-    AK_CUDA(cudaEventCreate(&ev_g1_));
+    for (Bank& b : banks_) {
+        AK_CUDA(cudaEventCreate(&b.ev_attn0));
+        AK_CUDA(cudaEventCreate(&b.ev_attn1));
+        AK_CUDA(cudaEventCreate(&b.ev_g0));
+        AK_CUDA(cudaEventCreate(&b.ev_g1));
+        AK_CUDA(cudaEventCreateWithFlags(&b.ev_done, cudaEventDisableTiming));
+    }
+    ev_attn0_ = banks_[0].ev_attn0; ev_attn1_ = banks_[0].ev_attn1; ev_g0_ = banks_[0].ev_g0; ev_g1_ = banks_[0].ev_g1;
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -387,20 +379,15 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
     bool pending = false;  // tp_tmp_ holds a reduced projection not yet added to hidden_
     int rc;
 #define RC(x) do { rc = (x); if (rc) return rc; trace_mark(#x); } while (0)
-    gtrace_capture_ = capturing && T == max_seqs_;
+    gtrace_capture_ = capturing && T == max_seqs_ && bank_ == 0;
     trace_mark("begin");
-    RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T, fuse_norm_ ? hb_ : nullptr));
+    RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
     for (uint32_t l = 0; l < c.num_layers; l++) {
         const auto& b = w_->blocks[l];
-        if (fuse_norm_) {
-            // norm_1 lives in the projection: gain folded into the weight, 1/rms applied in the epilogue
-            RC(launch_gemm_bf16_ex(st, hb_, qkv_f_[l], qkv_, T, 3 * Dq, D, AK_EPI_STORE_F32, 3 * Dq, true, nullptr, true, c.norm_eps));
-        } else {
-            if (pending) RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_1, xn_, nullptr, T, D, c.norm_eps, 0, dt));
-            else RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
-            pending = false;
-            RC(gemm(xn_, b.qkv, qkv_, T, 3 * Dq, D, 0));
-        }
+        if (pending) RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_1, xn_, nullptr, T, D, c.norm_eps, 0, dt));
+        else RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
+        pending = false;
+        RC(gemm(xn_, b.qkv, qkv_, T, 3 * Dq, D, 0));
         RC(launch_rope_kv_append(st, qkv_, rows + 1, rows + 2, 4, qbuf_, k_pool_[l], v_pool_[l], rope_table_, rope_len_, T, H, hd, 16, dt));
         if (any_decode) {
             ak_attn_decode_params p{};
@@ -429,20 +416,15 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
             RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));
             RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
             RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_2, xn_, nullptr, T, D, c.norm_eps, 0, dt));
-        } else if (fuse_norm_) {
-            RC(launch_gemm_bf16_ex(st, attn_, b.out, hidden_, T, D, Dq, AK_EPI_ADD_F32, D, true, hb_, false, 0.0f));
         } else {
             RC(gemm(attn_, b.out, hidden_, T, D, Dq, 1));
             RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
         }
-        if (fuse_norm_) RC(launch_gemm_bf16_ex(st, hb_, up_f_[l], up_, T, F, D, AK_EPI_SILU_BF16, F, true, nullptr, true, c.norm_eps));
-        else RC(gemm(xn_, b.up, up_, T, F, D, 2));
+        RC(gemm(xn_, b.up, up_, T, F, D, 2));
         if (tp) {
             RC(gemm(up_, b.down, tp_tmp_, T, D, F, 0));
             RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
             pending = true;
-        } else if (fuse_norm_) {
-            RC(launch_gemm_bf16_ex(st, up_, b.down, hidden_, T, D, F, AK_EPI_ADD_F32, D, true, hb_, false, 0.0f));
         } else {
             RC(gemm(up_, b.down, hidden_, T, D, F, 1));
         }
@@ -513,7 +495,7 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
         int32_t* pfs = h_pf_slot();
         for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; }
     }
-    const uint64_t key = ((uint64_t)rows_b << 32) | seqs_b;
+    const uint64_t key = ((uint64_t)bank_ << 63) | ((uint64_t)rows_b << 32) | seqs_b;  // a graph bakes its bank's host buffers and events
     const uint32_t T = max_seqs_ + rows_b;
     const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
     const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
@@ -545,7 +527,7 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
         AK_CUDA(cudaGraphInstantiate(&g.exec, graph, 0));
         cudaGraphDestroy(graph);
         graphs_[key] = g;
-        if (key == 0) graph_kernels = g.kernels;
+        if ((key << 1) == 0) graph_kernels = g.kernels;
         return AK_OK;
     }
     if (attn_timing_) AK_CUDA(cudaEventRecord(ev_g0_, st));
@@ -558,6 +540,29 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
     g_launch_count += it->second.kernels;
     h2d_bytes += it->second.h2d;
     d2h_bytes += (size_t)max_seqs_ * 4;
+    return AK_OK;
+}
+
+void Runner::set_bank(uint32_t b) {
+    b &= 1u;
+    if (b == bank_) return;
+    banks_[bank_].ev_valid = ev_valid_;
+    banks_[bank_].ev_g_valid = ev_g_valid_;
+    bank_ = b;
+    const Bank& k = banks_[b];
+    h_desc_ = k.h_desc; h_sampled_ = k.h_sampled;
+    ev_attn0_ = k.ev_attn0; ev_attn1_ = k.ev_attn1; ev_g0_ = k.ev_g0; ev_g1_ = k.ev_g1;
+    ev_valid_ = k.ev_valid; ev_g_valid_ = k.ev_g_valid;
+}
+
+int Runner::mark_done() {
+    AK_CUDA(cudaEventRecord(banks_[bank_].ev_done, ctx_->stream));
+    return AK_OK;
+}
+
+int Runner::wait_bank(uint32_t b) {
+    trace_dump();
+    AK_CUDA(cudaEventSynchronize(banks_[b & 1u].ev_done));
     return AK_OK;
 }
 

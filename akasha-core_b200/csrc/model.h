@@ -88,6 +88,14 @@ class Runner {
     // Any step (decode rows + optional prefill rows) through a per-bucket captured graph.
     int run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len);
     int sync();
+    // Two banks of host-side step state (pinned descriptor, pinned result buffer, timing events, captured
+    // graphs), so that the host can describe and launch step N+1 while step N is still running. The
+    // accessors above and run()/run_graph() use the current bank; the device buffers are shared and
+    // ordered by the stream.
+    void set_bank(uint32_t b);
+    uint32_t bank() const { return bank_; }
+    int mark_done();               // record "the step launched from the current bank is complete"
+    int wait_bank(uint32_t b);     // block until the step last launched from bank b is complete
     int read_logits(uint32_t slot, float* host_out);
     int gather_cache(uint32_t layer, const int32_t* h_table, uint32_t len, float* k_out, float* v_out);
 
@@ -125,12 +133,6 @@ class Runner {
     void* qbuf_ = nullptr;
     void* attn_ = nullptr;
     void* up_ = nullptr;
-    // bf16, single GPU: the per-layer RMSNorms are folded into the projections that follow them. hb_ is
-    // a bf16 copy of the residual stream (written by the embedding and by the out-proj / ffn-down
-    // epilogues); qkv_f_/up_f_ are the qkv / ffn-up weights with the norm gain multiplied in.
-    bool fuse_norm_ = false;
-    void* hb_ = nullptr;
-    std::vector<void*> qkv_f_, up_f_;
     void* xf_ = nullptr;
     float* logits_ = nullptr;
     uint32_t logits_ld_ = 0;          // row pitch of logits_ (padded to 4 in bf16 mode)
@@ -163,6 +165,13 @@ class Runner {
     void trace_mark(const char* label);
     void trace_dump();
     bool ev_valid_ = false;
+    struct Bank {
+        int32_t* h_desc = nullptr;
+        uint32_t* h_sampled = nullptr;
+        cudaEvent_t ev_attn0 = nullptr, ev_attn1 = nullptr, ev_g0 = nullptr, ev_g1 = nullptr, ev_done = nullptr;
+        bool ev_valid = false, ev_g_valid = false;
+    } banks_[2];
+    uint32_t bank_ = 0;
 };
 
 }  // namespace ak

@@ -155,11 +155,5 @@ def gemm_bf16(a, wt, c, m, n, k, epilogue=0, stream=None):
     check(lib().ak_gemm_bf16(_s(stream), _p(a), _p(wt), _p(c), MatMulMeta(m, n, k), epilogue))
 
 
-def gemm_bf16_ex(a, wt, c, m, n, k, epilogue=0, c_bf16_copy=None, rmsnorm_rows=False, eps=1e-5, stream=None):
-    """`gemm_bf16` with the bf16 copy of a `+=` result and/or the per-row RMSNorm factor fused in."""
-    check(lib().ak_gemm_bf16_ex(_s(stream), _p(a), _p(wt), _p(c), MatMulMeta(m, n, k), epilogue, _p(c_bf16_copy),
-                                1 if rmsnorm_rows else 0, eps))
-
-
 def transpose_to_bf16(w_kn, wt_nk, k, n, stream=None):
     check(lib().ak_transpose_to_bf16(_s(stream), _p(w_kn), _p(wt_nk), k, n))

@@ -52,7 +52,7 @@ def main():
     prompts = [ak.uniform_tokens(int(lens[i]), cfg.vocab_size, seed=50_000 + i) for i in mine]
     max_len = 3072 + gen
     eng = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=max_len, max_batch_tokens=max_seqs + 16384,
-                    use_cuda_graph=True, attn_timing=True)
+                    use_cuda_graph=True, attn_timing=True, async_steps=(tp == 1))
 
     def job():
         ids = [eng.submit(p, len(p) + gen) for p in prompts]

@@ -241,16 +241,6 @@ typedef enum ak_gemm_epilogue {
 } ak_gemm_epilogue;
 AK_API int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue);
 
-/* ak_gemm_bf16 with two fusions the engine uses in bf16 mode (no reference counterpart: they replace
- * the separate RMSNORM nodes of the layer graphs, src/nn/inference_graphs.rs:222-236, 300-314):
- *   c_bf16_copy  (AK_EPI_ADD_F32 only, may be NULL): bf16 [m, n] copy of the updated C rows, i.e. the
- *                residual stream as the next projection's activation;
- *   rmsnorm_rows != 0: every output row i is scaled by 1/sqrt(mean_k(A[i,k]^2) + eps) before the
- *                epilogue op, the mean taken over the bf16 activation row the tensor core consumed.
- *                With the norm's gain multiplied into Wt (Wt[n,k] * gain[k]) this is
- *                rmsnorm(A) @ W without a normalisation kernel and without the normalised copy. */
-AK_API int ak_gemm_bf16_ex(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue,
-                           void* c_bf16_copy, uint32_t rmsnorm_rows, float eps);
 /* Make the [n,k] bf16 operand from a reference-layout f32 [k,n] matrix (device to device). */
 AK_API int ak_transpose_to_bf16(void* stream, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);
 AK_API int ak_f32_to_bf16(void* stream, const float* src, void* dst, uint64_t n);
@@ -343,6 +333,11 @@ typedef struct ak_engine_config {
     uint32_t use_cuda_graph;   /* capture the decode-only step in a CUDA graph      */
     uint32_t stop_on_eos;      /* 0: run every sequence to its max_len              */
     uint32_t attn_timing;      /* record CUDA events around layer 0's decode attention */
+    uint32_t async_steps;      /* 1: ak_engine_step returns once step N is LAUNCHED and step N-1's tokens are on the
+                                * host, so describing and launching a step overlaps the previous step's GPU time.
+                                * Needs stop_on_eos == 0 (sequence ends must be known without the tokens);
+                                * ignored otherwise. poll / block_table / get_stats / clear_finished / run wait for
+                                * the step in flight first. */
 } ak_engine_config;
 
 AK_API int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak_engine** out);
@@ -353,6 +348,10 @@ AK_API int ak_engine_submit(ak_engine* e, const uint32_t* prompt, uint32_t n, ui
  * this step's ragged batch), run one token for every running sequence, retire finished ones.
  * n_running / n_finished_total may be NULL. Returns after the step's token ids are on the host. */
 AK_API int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting);
+/* Steps until nothing is running or waiting (at most max_steps; 0 = no limit), then waits for the last
+ * step. steps_done may be NULL. The loop the reference's `generate` runs per sequence
+ * (src/nn/inference.rs:264-326), for the whole queue and without returning to the caller per token. */
+AK_API int ak_engine_run(ak_engine* e, uint64_t max_steps, uint64_t* steps_done);
 /* Has the sequence finished? Its generated tokens (prompt excluded) are copied to out (capacity
  * cap); n_out gets the count generated so far. */
 AK_API int ak_engine_poll(ak_engine* e, uint64_t seq_id, uint32_t* out, uint32_t cap, uint32_t* n_out, int* finished);

@@ -191,46 +191,6 @@ def test_gemm_bf16_epilogues(ak, orc, torch_cuda, epi, m, n, k):
     assert np.max(np.abs(host(c) - want)) < tol
 
 
-@pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (64, 3072, 768), (7, 768, 768), (200, 3072, 768), (600, 2304, 768), (64, 6144, 2048),
-                                   (300, 2048, 8192)])
-def test_gemm_bf16_fused_rmsnorm(ak, orc, torch_cuda, m, n, k):
-    """Output rows scaled by the RMSNorm factor of their bf16 activation row (the factor is computed
-    inside the GEMM from the staged tiles): every plan (cluster split-K, in-CTA segments, plain)."""
-    torch = torch_cuda
-    a = bf16_round(orc, (orc.lcg(m * k, 13) * np.float32(3.0)).reshape(m, k))
-    a *= (1.0 + np.arange(m, dtype=np.float32)[:, None] * 0.05)      # rows of different scale
-    a = bf16_round(orc, a)
-    w = bf16_round(orc, (orc.lcg(k * n, 14) * np.float32(0.2)).reshape(k, n))
-    da = torch.from_numpy(a).cuda().bfloat16()
-    wt = torch.from_numpy(np.ascontiguousarray(w.T)).cuda().bfloat16()
-    eps = 1e-5
-    rstd = 1.0 / np.sqrt((a.astype(np.float64) ** 2).mean(axis=1) + eps)
-    want = (a.astype(np.float64) @ w.astype(np.float64)) * rstd[:, None]
-    c = torch.full((m, n), float("nan"), device="cuda", dtype=torch.float32)
-    ak.ops.gemm_bf16_ex(da, wt, c, m, n, k, ak.EPI_STORE_F32, None, True, eps)
-    torch.cuda.synchronize()
-    ak.check(ak.lib().ak_check_device_status(None))
-    assert np.max(np.abs(host(c) - want)) < 2e-4 * np.sqrt(k) * max(1.0, np.abs(want).max())
-
-
-def test_gemm_bf16_add_with_bf16_copy(ak, orc, torch_cuda):
-    """`+=` epilogue that also leaves a bf16 copy of the updated rows (the next projection's input)."""
-    torch = torch_cuda
-    for m, n, k in [(64, 768, 768), (64, 768, 3072), (300, 768, 3072), (700, 768, 768)]:
-        a = bf16_round(orc, orc.lcg(m * k, 3).reshape(m, k))
-        w = bf16_round(orc, (orc.lcg(k * n, 4) * np.float32(0.2)).reshape(k, n))
-        c0 = orc.lcg(m * n, 5).reshape(m, n)
-        da = torch.from_numpy(a).cuda().bfloat16()
-        wt = torch.from_numpy(np.ascontiguousarray(w.T)).cuda().bfloat16()
-        c = torch.from_numpy(c0).cuda()
-        cb = torch.full((m, n), float("nan"), device="cuda", dtype=torch.bfloat16)
-        ak.ops.gemm_bf16_ex(da, wt, c, m, n, k, ak.EPI_ADD_F32, cb, False, 0.0)
-        torch.cuda.synchronize()
-        want = c0 + a.astype(np.float64) @ w.astype(np.float64)
-        assert np.max(np.abs(host(c) - want)) < 1e-4 * np.sqrt(k) + 1e-5
-        assert torch.equal(cb, c.bfloat16()), "the copy is the f32 result rounded once"
-
-
 def ref_prefill(orc, q, k, v, hd):
     """Causal attention of one sequence (q/k/v [L, dim]) with the oracle's flash attention."""
     return orc.flash_attention(np.ascontiguousarray(q), np.ascontiguousarray(k), np.ascontiguousarray(v), hd)

@@ -194,8 +194,9 @@ def test_akasha_hall_config1_parity(ak, orc, ctx):
 
 
 # ================================================================================ engine
-def run_engine(ak, ctx, w, prompts, total_len, max_seqs, graph, max_seq_len=None):
-    e = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=max_seq_len or total_len, use_cuda_graph=graph)
+def run_engine(ak, ctx, w, prompts, total_len, max_seqs, graph, max_seq_len=None, async_steps=False):
+    e = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=max_seq_len or total_len, use_cuda_graph=graph,
+                  async_steps=async_steps)
     ids = [e.submit(p, total_len) for p in prompts]
     steps = e.run_to_completion(100000)
     outs, tables = [], []
@@ -272,6 +273,40 @@ def test_engine_bf16_batch_invariance_and_oracle_agreement(ak, orc, ctx):
     print(f"bf16 engine vs bf16-emulating oracle: {agree}/{total_tok} tokens agree before first divergence")
     assert agree / total_tok > 0.5
     w.close()
+
+
+@pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
+def test_engine_async_steps_equal_sync_steps(ak, ctx, dtype_name):
+    """One step in flight while the next is described and launched: same tokens, same block
+    tables, same step count as the synchronous engine (ragged prompts, more sequences than slots, so
+    slots are retired and refilled while a step is in flight); stepping by hand and polling mid-run
+    sees only complete tokens."""
+    cfg = ak.ModelConfig(600, 128, 2, 2, 96)
+    dt = ak.AK_F32 if dtype_name == "f32" else ak.AK_BF16
+    _, w = make(ak, ctx, cfg, 0, 0.06, dt)
+    total, max_seqs, n = 96, 4, 13
+    lens = ak.uniform_ints(n, 3, 60, seed=7)
+    prompts = [ak.uniform_tokens(int(l), cfg.vocab_size, seed=300 + i) for i, l in enumerate(lens)]
+    a_out, a_tab, a_st, a_steps = run_engine(ak, ctx, w, prompts, total, max_seqs, True, async_steps=True)
+    s_out, s_tab, s_st, s_steps = run_engine(ak, ctx, w, prompts, total, max_seqs, True, async_steps=False)
+    assert a_steps == s_steps
+    for a, b in zip(a_out, s_out):
+        assert a.tolist() == b.tolist()
+    for a, b in zip(a_tab, s_tab):
+        assert a.tolist() == b.tolist()
+    assert a_st["decode_tokens"] == s_st["decode_tokens"] and a_st["prefill_tokens"] == s_st["prefill_tokens"]
+    # by hand: poll in the middle of the run
+    e = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=total, use_cuda_graph=True, async_steps=True)
+    ids = [e.submit(p, total) for p in prompts]
+    for _ in range(7):
+        e.step()
+    t, fin = e.poll(ids[0])
+    assert len(t) == 7 and not fin and t.tolist() == s_out[0][:7].tolist()
+    e.run_to_completion(100000)
+    for i, want in zip(ids, s_out):
+        t, fin = e.poll(i)
+        assert fin and t.tolist() == want.tolist()
+    e.close(); w.close()
 
 
 def test_engine_capacity_and_errors(ak, ctx):
