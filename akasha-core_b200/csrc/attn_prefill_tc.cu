@@ -22,7 +22,7 @@ __device__ unsigned int g_prefill_tc_status = 0;
 
 namespace pftc {
 
-constexpr int BQ = 128, BKV = 64, BS = 16, THREADS = 128;
+constexpr int BQ = 128, BS = 16, THREADS = 128;
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
@@ -80,22 +80,25 @@ __host__ __device__ constexpr uint32_t idesc(uint32_t m, uint32_t n, uint32_t b_
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-template <int HD> struct Cfg {
+// BKV = keys per step = N of the QK^T instruction. One tcgen05.mma costs about the same for N = 64 and
+// N = 128, and every step pays fixed latencies (commit -> wait, two CTA barriers), so wider is better
+// until shared memory runs out.
+template <int HD, int BKV> struct Cfg {
     static constexpr int HALVES = HD / 64;                 // 64-column (128-byte) slabs per row
     static constexpr int Q_BYTES = BQ * HD * 2;            // HALVES slabs of [128 x 64]
-    static constexpr int KV_BYTES = BKV * HD * 2;          // HALVES slabs of [64 x 64]
-    static constexpr int P_BYTES = BQ * BKV * 2;           // [128 x 64]
+    static constexpr int KV_BYTES = BKV * HD * 2;          // HALVES slabs of [BKV x 64]
+    static constexpr int P_BYTES = BQ * BKV * 2;           // BKV/64 slabs of [128 x 64]
     static constexpr int SMEM_BYTES = Q_BYTES + 2 * 2 * KV_BYTES + P_BYTES + 1024;
-    static constexpr int TMEM_COLS = (64 + HD) <= 128 ? 128 : 256;
+    static constexpr int TMEM_COLS = (BKV + HD) <= 128 ? 128 : ((BKV + HD) <= 256 ? 256 : 512);
 };
 
-template <int HD>
+template <int HD, int BKV>
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const int32_t* __restrict__ block_tables, uint32_t max_blocks,
                   const int32_t* __restrict__ cu, const int32_t* __restrict__ seq_slot, bf16* __restrict__ out, uint32_t row_base,
                   uint32_t heads, float scale) {
-    using C = Cfg<HD>;
+    using C = Cfg<HD, BKV>;
     pdl_wait();
     pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
@@ -124,7 +127,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_base_sm, tmem_pv = tmem_base_sm + 64;
+    const uint32_t tmem_s = tmem_base_sm, tmem_pv = tmem_base_sm + BKV;
     const uint32_t lane_addr = (warp * 32u) << 16;
 
     const uint32_t q_hi = (q0 + BQ - 1 < len - 1) ? q0 + BQ - 1 : len - 1;
@@ -236,9 +239,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 rs += __bfloat162float(v2.x) + __bfloat162float(v2.y);
                 pk[j / 2] = *reinterpret_cast<uint32_t*>(&v2);
             }
-            const uint32_t ch = c0 / 8;  // two 16-byte chunks per 16 columns
-            *reinterpret_cast<uint4*>(p_sm + tid * 128 + (((ch) ^ (tid & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(p_sm + tid * 128 + (((ch + 1) ^ (tid & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            uint8_t* p_row = p_sm + (c0 / 64) * (BQ * 128) + tid * 128;  // slab of 64 keys, this thread's row
+            const uint32_t ch = (c0 % 64) / 8;                           // two 16-byte chunks per 16 columns
+            *reinterpret_cast<uint4*>(p_row + (((ch) ^ (tid & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(p_row + (((ch + 1) ^ (tid & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
         l_run = l_run * corr + rs;
         m_run = m_new;
@@ -250,7 +254,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             // PV[128 x HD] = P[128 x 64] . V[64 x HD]   (V is the MN-major B operand)
 #pragma unroll
             for (int kk = 0; kk < BKV / 16; kk++)
-                tc_mma(tmem_pv, desc_kmajor(smem_u32(p_sm)) + kk * 2, desc_mnmajor(smem_u32(v_sm + kk * (16 * 128)), BKV * 128),
+                tc_mma(tmem_pv, desc_kmajor(smem_u32(p_sm + (kk / 4) * (BQ * 128))) + (kk % 4) * 2, desc_mnmajor(smem_u32(v_sm + kk * (16 * 128)), BKV * 128),
                        idesc(BQ, HD, 1), kk != 0);
             tc_commit(&pv_bar);
         }
@@ -295,11 +299,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     }
 }
 
-template <int HD>
+template <int HD, int BKV>
 static int launch(cudaStream_t st, const void* q, uint64_t q_rows, const void* k_pool, const void* v_pool, uint64_t pool_rows,
                   const int32_t* bt, uint32_t max_blocks, const int32_t* cu, const int32_t* seq_slot, void* out, uint32_t n_seqs,
                   uint32_t max_len, uint32_t row_base, uint32_t heads, float scale) {
-    using C = Cfg<HD>;
+    using C = Cfg<HD, BKV>;
     CUtensorMap tmQ, tmK, tmV;
     const uint64_t dim = (uint64_t)heads * HD;
     AK_TRY(make_tmap_2d(&tmQ, q, 2, dim, q_rows, dim * 2, 64, BQ, TMA_SWIZZLE_128B));
@@ -309,10 +313,10 @@ static int launch(cudaStream_t st, const void* q, uint64_t q_rows, const void* k
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
     if (!attr_set[dev & 63]) {
-        AK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        AK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<HD, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         attr_set[dev & 63] = true;
     }
-    return launch_k(prefill_tc_kernel<HD>, dim3(cdiv(max_len, BQ), heads, n_seqs), dim3(THREADS), C::SMEM_BYTES, st, NO_CLUSTER, tmQ, tmK,
+    return launch_k(prefill_tc_kernel<HD, BKV>, dim3(cdiv(max_len, BQ), heads, n_seqs), dim3(THREADS), C::SMEM_BYTES, st, NO_CLUSTER, tmQ, tmK,
                     tmV, bt, max_blocks, cu, seq_slot, (bf16*)out, row_base, heads, scale);
 }
 
@@ -324,10 +328,14 @@ int launch_attn_prefill_tc(cudaStream_t st, const void* q, uint64_t q_rows, cons
                            uint32_t head_dim, float scale) {
     if (n_seqs == 0 || max_len == 0) return AK_OK;
     const uint64_t pool_rows = pool_blocks * heads * pftc::BS;
-    if (head_dim == 64)
-        return pftc::launch<64>(st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, row_base, heads, scale);
+    // keys per step: 128 for head_dim 64 (a little faster); 64 for head_dim 128, where 128 would leave room for
+    // one CTA per SM only (measured slower on long prompts). AK_PREFILL_BKV=64|128 forces one, for comparison.
+    static const int forced = [] { const char* e = getenv("AK_PREFILL_BKV"); return e ? atoi(e) : 0; }();
+#define AK_PF_ARGS st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, row_base, heads, scale
+    if (head_dim == 64) return forced == 64 ? pftc::launch<64, 64>(AK_PF_ARGS) : pftc::launch<64, 128>(AK_PF_ARGS);
     AK_REQUIRE(head_dim == 128, AK_ERR_UNSUPPORTED, "prefill attention (tensor cores): head_dim must be 64 or 128");
-    return pftc::launch<128>(st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, row_base, heads, scale);
+    return forced == 128 ? pftc::launch<128, 128>(AK_PF_ARGS) : pftc::launch<128, 64>(AK_PF_ARGS);
+#undef AK_PF_ARGS
 }
 
 int prefill_tc_status(unsigned int* out) {
