@@ -246,7 +246,10 @@ __device__ __forceinline__ void epi_store16(const GemmEpi& ep, uint32_t row, boo
 // distributed shared memory (every CTA receives the column slice it owns from every peer) and
 // each reduces and stores its own slice in a fixed source order, so the result does not depend on
 // timing. ks == 1 is the plain one-CTA-per-tile GEMM.
-template <int BN, int EPI>
+// SPLIT selects, at compile time, the cluster exchange epilogue (true) or the one-CTA-per-tile epilogue
+// (false): a decode step is a chain of short launches whose first wave also pays for fetching the kernel's
+// instructions, so each instantiation carries only the path it runs.
+template <int BN, int EPI, bool SPLIT>
 __global__ void __launch_bounds__(G_THREADS)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmEpi ep,
                  uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tmem_cols, uint32_t a_rows) {
@@ -263,8 +266,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     __shared__ uint32_t fail_flag;
 
     cg::cluster_group cluster = cg::this_cluster();
-    const uint32_t ks = cluster.num_blocks();
-    const uint32_t rank = cluster.block_rank();
+    const uint32_t ks = SPLIT ? cluster.num_blocks() : 1u;
+    const uint32_t rank = SPLIT ? cluster.block_rank() : 0u;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     float* red = reinterpret_cast<float*>(smem + (size_t)stages * C::STAGE_BYTES);  // used when ks > 1
@@ -292,7 +295,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // memory. Arrive now, wait only right before the exchange: the barrier latency hides behind
     // the main loop.
     __syncthreads();
-    if (ks > 1) cluster_arrive_all();
+    if (SPLIT) cluster_arrive_all();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_sm;
     // Everything above touched only this CTA's shared memory and TMEM. Let the next kernel's blocks
@@ -366,7 +369,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tc_fence_after();
     }
 
-    if (ks == 1) {
+    if (!SPLIT) {
         if (warp >= 2 && got) {
             float best = -INFINITY;
             uint32_t best_i = 0xffffffffu;
@@ -599,13 +602,17 @@ static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
     if (attr_set[dev & 63] < smem) {
-        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
         attr_set[dev & 63] = SMEM_ONE_PER_SM;
     }
     uint32_t need = p.kseg * BN, cols = 32;
     while (cols < need) cols *= 2;
     AK_REQUIRE(cols <= 512, AK_ERR_UNSUPPORTED, "gemm_bf16: %u accumulator columns exceed TMEM", need);
-    return launch_k(gemm_bf16_kernel<BN, EPI>, dim3(cdiv(n, BN), cdiv(m, GB_M), p.ks), dim3(G_THREADS), smem, st, dim3(1, 1, p.ks),
+    if (p.ks > 1)
+        return launch_k(gemm_bf16_kernel<BN, EPI, true>, dim3(cdiv(n, BN), cdiv(m, GB_M), p.ks), dim3(G_THREADS), smem, st, dim3(1, 1, p.ks),
+                        tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols, a_box_rows(m));
+    return launch_k(gemm_bf16_kernel<BN, EPI, false>, dim3(cdiv(n, BN), cdiv(m, GB_M), 1), dim3(G_THREADS), smem, st, dim3(1, 1, 1),
                     tmA, tmB, ep, m, n, k, p.stages, p.kseg, cols, a_box_rows(m));
 }
 

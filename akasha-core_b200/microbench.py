@@ -59,7 +59,8 @@ def bench_attn(ak, torch, iters, small):
     rows = int(_opt("--rows", rows))
     splits = int(_opt("--splits", 1))
     lo = int(_opt("--min-len", 1))
-    lens = ak.uniform_ints(rows, lo, 512, seed=3)
+    hi = int(_opt("--max-len", 512))
+    lens = ak.uniform_ints(rows, lo, hi, seed=3)
     n_blocks = rows * max_blocks
     g = torch.Generator(device="cuda").manual_seed(3)
     kp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
