@@ -106,7 +106,9 @@ def cpu_reference_arm(ak, steps: int, warmup: int, sample_seqs: int = 2, decode_
     params = ak.synthetic_weights(cfg, seed=0, std=0.02)
     model = orc.Model(cfg.as_dict(), params)
     prompts = make_prompts(ak, 0)[:sample_seqs]
-    cores = orc.max_threads()
+    # every core this process may run on (a launcher may have exported OMP_NUM_THREADS=1: the oracle's own
+    # maximum would then read 1)
+    cores = max(orc.max_threads(), len(os.sched_getaffinity(0)))
     orc.set_threads(cores)
 
     def one_pass():
