@@ -230,6 +230,9 @@ Runner::~Runner() {
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    if (ev_fork_) cudaEventDestroy(ev_fork_);
+    if (ev_join_) cudaEventDestroy(ev_join_);
+    if (st2_) cudaStreamDestroy(st2_);
     for (Bank& b : banks_) {
         if (b.ev_attn0) cudaEventDestroy(b.ev_attn0);
         if (b.ev_attn1) cudaEventDestroy(b.ev_attn1);
@@ -348,6 +351,13 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
         AK_CUDA(cudaEventCreateWithFlags(&b.ev_done, cudaEventDisableTiming));
     }
     ev_attn0_ = banks_[0].ev_attn0; ev_attn1_ = banks_[0].ev_attn1; ev_g0_ = banks_[0].ev_g0; ev_g1_ = banks_[0].ev_g1;
+    AK_CUDA(cudaStreamCreateWithFlags(&st2_, cudaStreamNonBlocking));
+    AK_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+    AK_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
+    {
+        const char* e = getenv("AK_TWO_STREAMS");
+        two_streams_ = !(e && e[0] == '0');
+    }
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -381,52 +391,124 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
 #define RC(x) do { rc = (x); if (rc) return rc; trace_mark(#x); } while (0)
     gtrace_capture_ = capturing && T == max_seqs_ && bank_ == 0;
     trace_mark("begin");
-    RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
-    for (uint32_t l = 0; l < c.num_layers; l++) {
-        const auto& b = w_->blocks[l];
-        if (pending) RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_1, xn_, nullptr, T, D, c.norm_eps, 0, dt));
-        else RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
-        pending = false;
-        RC(gemm(xn_, b.qkv, qkv_, T, 3 * Dq, D, 0));
-        RC(launch_rope_kv_append(st, qkv_, rows + 1, rows + 2, 4, qbuf_, k_pool_[l], v_pool_[l], rope_table_, rope_len_, T, H, hd, 16, dt));
-        if (any_decode) {
-            ak_attn_decode_params p{};
-            p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
-            p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
-            const bool timed = attn_timing_ && l == 0;
-            if (timed) {
-                if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, st, cudaEventRecordExternal));
-                else AK_CUDA(cudaEventRecord(ev_attn0_, st));
+    if (!tp) {
+        // One range of rows through every layer on one stream. Decode rows are [0, max_seqs_), prompt rows
+        // follow; the two kinds never read each other's rows, so an admission step runs them as two
+        // ranges on two streams, joined before the final norm.
+        const size_t act = dt == AK_F32 ? 4 : 2;
+        auto gemm_s = [&](cudaStream_t s, const void* a, const void* wt, void* cc, uint32_t m, uint32_t n, uint32_t k, int mode) -> int {
+            if (dt == AK_F32) {
+                const uint32_t flags = mode == 1 ? GEMM_ADD : (mode == 2 ? GEMM_SILU : 0);
+                return launch_gemm_f32(s, (const float*)a, (const float*)wt, (float*)cc, m, n, k, flags);
             }
-            g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
-            rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
-            g_attn_early = false;
+            const uint32_t epi = mode == 1 ? AK_EPI_ADD_F32 : (mode == 2 ? AK_EPI_SILU_BF16 : AK_EPI_STORE_F32);
+            return launch_gemm_bf16(s, a, wt, cc, m, n, k, epi, n, true);
+        };
+        auto range = [&](cudaStream_t s, uint32_t r0, uint32_t nr, bool dec, bool pf) -> int {
+            const int32_t* rw = rows + (size_t)r0 * 4;
+            float* hid = hidden_ + (size_t)r0 * D;
+            void* xn = (char*)xn_ + (size_t)r0 * D * act;
+            float* qkv = qkv_ + (size_t)r0 * 3 * Dq;
+            void* qb = (char*)qbuf_ + (size_t)r0 * Dq * act;
+            void* at = (char*)attn_ + (size_t)r0 * Dq * act;
+            void* up = (char*)up_ + (size_t)r0 * F * act;
+            RC(launch_embed_rows(s, rw + 0, 4, d_sampled_, w_->embedding, dt, hid, V, D, nr));
+            for (uint32_t l = 0; l < c.num_layers; l++) {
+                const auto& b = w_->blocks[l];
+                RC(launch_rmsnorm(s, hid, b.norm_1, xn, dt, nullptr, nr, D, c.norm_eps));
+                RC(gemm_s(s, xn, b.qkv, qkv, nr, 3 * Dq, D, 0));
+                RC(launch_rope_kv_append(s, qkv, rw + 1, rw + 2, 4, qb, k_pool_[l], v_pool_[l], rope_table_, rope_len_, nr, H, hd, 16, dt));
+                if (dec) {  // rows [0, max_seqs_): this range starts at row 0
+                    ak_attn_decode_params p{};
+                    p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
+                    p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
+                    const bool timed = attn_timing_ && l == 0;
+                    if (timed) {
+                        if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, s, cudaEventRecordExternal));
+                        else AK_CUDA(cudaEventRecord(ev_attn0_, s));
+                    }
+                    g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
+                    rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
+                    g_attn_early = false;
+                    if (rc) return rc;
+                    if (timed) {
+                        if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, s, cudaEventRecordExternal));
+                        else AK_CUDA(cudaEventRecord(ev_attn1_, s));
+                        ev_valid_ = true;
+                    }
+                }
+                if (pf && n_pf_seqs) {  // prompt rows are addressed from row max_seqs_ of the full buffers
+                    RC(launch_attn_prefill_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
+                                                 d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
+                }
+                RC(gemm_s(s, at, b.out, hid, nr, D, Dq, 1));
+                RC(launch_rmsnorm(s, hid, b.norm_2, xn, dt, nullptr, nr, D, c.norm_eps));
+                RC(gemm_s(s, xn, b.up, up, nr, F, D, 2));
+                RC(gemm_s(s, up, b.down, hid, nr, D, F, 1));
+            }
+            return AK_OK;
+        };
+        if (two_streams_ && any_decode && T > max_seqs_ && n_pf_seqs) {
+            AK_CUDA(cudaEventRecord(ev_fork_, st));
+            AK_CUDA(cudaStreamWaitEvent(st2_, ev_fork_, 0));
+            rc = range(st, 0, max_seqs_, true, false);
             if (rc) return rc;
-            if (timed) {
-                if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, st, cudaEventRecordExternal));
-                else AK_CUDA(cudaEventRecord(ev_attn1_, st));
-                ev_valid_ = true;
+            rc = range(st2_, max_seqs_, T - max_seqs_, false, true);
+            if (rc) return rc;
+            AK_CUDA(cudaEventRecord(ev_join_, st2_));
+            AK_CUDA(cudaStreamWaitEvent(st, ev_join_, 0));
+        } else {
+            rc = range(st, 0, T, any_decode, true);
+            if (rc) return rc;
+        }
+    } else {
+        RC(launch_embed_rows(st, rows + 0, 4, d_sampled_, w_->embedding, dt, hidden_, V, D, T));
+        for (uint32_t l = 0; l < c.num_layers; l++) {
+            const auto& b = w_->blocks[l];
+            if (pending) RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_1, xn_, nullptr, T, D, c.norm_eps, 0, dt));
+            else RC(launch_rmsnorm(st, hidden_, b.norm_1, xn_, dt, nullptr, T, D, c.norm_eps));
+            pending = false;
+            RC(gemm(xn_, b.qkv, qkv_, T, 3 * Dq, D, 0));
+            RC(launch_rope_kv_append(st, qkv_, rows + 1, rows + 2, 4, qbuf_, k_pool_[l], v_pool_[l], rope_table_, rope_len_, T, H, hd, 16, dt));
+            if (any_decode) {
+                ak_attn_decode_params p{};
+                p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
+                p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
+                const bool timed = attn_timing_ && l == 0;
+                if (timed) {
+                    if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, st, cudaEventRecordExternal));
+                    else AK_CUDA(cudaEventRecord(ev_attn0_, st));
+                }
+                g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
+                rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
+                g_attn_early = false;
+                if (rc) return rc;
+                if (timed) {
+                    if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, st, cudaEventRecordExternal));
+                    else AK_CUDA(cudaEventRecord(ev_attn1_, st));
+                    ev_valid_ = true;
+                }
             }
-        }
-        if (n_pf_seqs) {
-            RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
-                                         d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
-        }
-        if (tp) {
-            RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));
-            RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
-            RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_2, xn_, nullptr, T, D, c.norm_eps, 0, dt));
-        } else {
-            RC(gemm(attn_, b.out, hidden_, T, D, Dq, 1));
-            RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
-        }
-        RC(gemm(xn_, b.up, up_, T, F, D, 2));
-        if (tp) {
-            RC(gemm(up_, b.down, tp_tmp_, T, D, F, 0));
-            RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
-            pending = true;
-        } else {
-            RC(gemm(up_, b.down, hidden_, T, D, F, 1));
+            if (n_pf_seqs) {
+                RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
+                                             d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
+            }
+            if (tp) {
+                RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));
+                RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
+                RC(launch_rmsnorm_rope_residual(st, hidden_, tp_tmp_, b.norm_2, xn_, nullptr, T, D, c.norm_eps, 0, dt));
+            } else {
+                RC(gemm(attn_, b.out, hidden_, T, D, Dq, 1));
+                RC(launch_rmsnorm(st, hidden_, b.norm_2, xn_, dt, nullptr, T, D, c.norm_eps));
+            }
+            RC(gemm(xn_, b.up, up_, T, F, D, 2));
+            if (tp) {
+                RC(gemm(up_, b.down, tp_tmp_, T, D, F, 0));
+                RC(tp_all_reduce_f32(ctx_, tp_tmp_, (size_t)T * D));
+                pending = true;
+            } else {
+                RC(gemm(up_, b.down, hidden_, T, D, F, 1));
+            }
         }
     }
     if (pending)  // fold the last ffn-down sum into the residual stream (the normalised output is not used)
