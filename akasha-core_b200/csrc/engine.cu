@@ -51,6 +51,7 @@ struct ak_engine {
         std::vector<std::pair<Seq*, uint32_t>> fill;  // (sequence, index into its `generated`), slot = seq->slot at launch
         std::vector<uint32_t> fill_slot;
         bool any_decode = false;
+        bool has_prefill = false;
         uint64_t attn_bytes = 0;
     } pending;
     uint64_t step_index = 0;
@@ -75,7 +76,8 @@ static int collect(ak_engine* e) {
         if (e->cfg.stop_on_eos && tok == mc.eos_token) s->finished = true;
     }
     if (e->cfg.attn_timing) e->stats.step_gpu_ms_total += r.last_step_gpu_ms();
-    if (e->cfg.attn_timing && p.any_decode) {
+    // the roofline sample: decode-only steps (in an admission step the prompt's kernels run beside the attention)
+    if (e->cfg.attn_timing && p.any_decode && !p.has_prefill) {
         float ms = r.last_attn_ms();
         if (ms > 0.0f) {
             e->stats.attn_ms_total += ms;
@@ -268,6 +270,7 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     now.active = true;
     now.bank = r.bank();
     now.any_decode = any_decode;
+    now.has_prefill = pf_rows != 0;
     now.attn_bytes = attn_bytes;
     uint32_t running = 0;
     for (uint32_t i = 0; i < S; i++) {

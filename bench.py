@@ -264,7 +264,7 @@ def main():
                     "h2d_bytes_per_step": (st2["h2d_bytes"] - st["h2d_bytes"]) / args.steps,
                     "d2h_bytes_per_step": (st2["d2h_bytes"] - st["d2h_bytes"]) / args.steps},
             "gpu_launches": int(st["kernel_launches"]),
-            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,2> (layer 0, every decode step)",
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,2> (layer 0, every decode-only step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind,
                          # DRAM bytes per launch: 1.059 x the algorithmic bytes, the ratio ncu measured
