@@ -1,16 +1,16 @@
 // Causal varlen prefill attention on the 5th-generation tensor cores (bf16 K/V/Q, fp32 softmax):
 // the same online-softmax recurrence as the reference's FLASH_ATTENTION kernel
-// (src/shaders/cuda.rs:633-685), tiled 128 queries x 64 keys.
+// (src/shaders/cuda.rs:633-685), tiled 128 queries x BKV keys (BKV = 64 or 128).
 //
 // One CTA (4 warps, thread <-> query row <-> TMEM lane) per (128-query tile, head, sequence):
-//   * TMA: the Q tile once; per step a 64-key K tile and V tile straight from the paged pools
-//     (4 blocks of 16 positions, 128-byte swizzle), double-buffered.
-//   * S = Q.K^T  : tcgen05.mma, A = Q (K-major), B = K tile (K-major), fp32 in TMEM columns [0,64).
+//   * TMA: the Q tile once; per step a BKV-key K tile and V tile straight from the paged pools
+//     (BKV/16 blocks of 16 positions, 128-byte swizzle), double-buffered.
+//   * S = Q.K^T  : tcgen05.mma, A = Q (K-major), B = K tile (K-major), fp32 in TMEM columns [0,BKV).
 //   * softmax    : each thread reads ITS row of S with tcgen05.ld (no cross-thread reduction),
 //                  applies scale + causal mask, updates running max / sum, writes P (bf16) into
 //                  shared memory in the swizzled K-major layout the next MMA reads.
 //   * PV = P.V   : tcgen05.mma, A = P, B = V tile used as an MN-major operand (V rows are keys, the
-//                  contiguous direction is head_dim), fp32 in TMEM columns [64, 64+head_dim).
+//                  contiguous direction is head_dim), fp32 in TMEM columns [BKV, BKV+head_dim).
 //   * O = O*corr + PV in registers; final O / sum -> bf16.
 // All mbarrier waits are bounded; on expiry a status word is set and the CTA unwinds.
 #include "kernels.h"
