@@ -28,6 +28,8 @@ struct Seq {
     uint32_t cached = 0;  // tokens whose K/V are in the cache
     int slot = -1;
     bool finished = false;
+    bool prefilling = false;   // admitted, its prompt is running as a detached prefill
+    int32_t pf_last_row = -1;  // row of its last prompt token in the runner's activation buffers
 };
 
 }  // namespace
@@ -55,6 +57,8 @@ struct ak_engine {
         uint64_t attn_bytes = 0;
     } pending;
     uint64_t step_index = 0;
+    bool pf_active = false;      // a detached prefill has been launched and has not joined yet
+    uint64_t pf_join_step = 0;   // the step in which its sequences sample their first token
     bool async_ok() const { return cfg.async_steps != 0 && cfg.stop_on_eos == 0; }
 };
 
@@ -175,7 +179,11 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     // 2. admit waiting sequences in arrival order into the lowest free slots
     std::vector<Seq*> admitted;
     uint32_t pf_rows = 0;
-    while (!e->waiting.empty()) {
+    const bool lag_ok = e->cfg.detached_prefill != 0 && e->cfg.use_cuda_graph != 0 && e->w->tp_size == 1;
+    const bool join_now = e->pf_active && e->step_index >= e->pf_join_step;
+    bool decoding_now = false;  // somebody is past its prompt: a new prompt can run beside the decode steps
+    for (uint32_t i = 0; i < S; i++) decoding_now |= (e->slots[i] && !e->slots[i]->finished && !e->slots[i]->prefilling);
+    while (!e->waiting.empty() && !(lag_ok && e->pf_active)) {
         Seq* s = e->waiting.front();
         int slot = -1;
         for (uint32_t i = 0; i < S; i++)
@@ -196,6 +204,12 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         admitted.push_back(s);
     }
 
+    const bool detach = lag_ok && !admitted.empty() && decoding_now;
+    if (detach) {
+        for (Seq* a : admitted) a->prefilling = true;
+        e->pf_active = true;
+        e->pf_join_step = e->step_index + 2;
+    }
     // 3. describe the step: decode rows by slot, then the admitted prompts
     RowInfo* rows = r.h_rows();
     int32_t* kv = r.h_kv_lens();
@@ -215,7 +229,7 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
             const uint32_t nb = (uint32_t)s->blocks.size();
             for (uint32_t b = 0; b < r.max_blocks(); b++) bt[b] = b < nb ? s->blocks[b] : 0;
         }
-        if (s && !is_new && !s->finished) {
+        if (s && !is_new && !s->finished && !s->prefilling) {
             const uint32_t pos = s->cached;
             rows[i] = {-(int32_t)(i + 1), (int32_t)pos, s->blocks[pos / 16] * 16 + (int32_t)(pos % 16), (int32_t)i};
             kv[i] = (int32_t)(pos + 1);
@@ -228,7 +242,8 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         } else {
             rows[i] = {INT_MIN, -1, -1, (int32_t)i};
             kv[i] = 0;
-            outr[i] = -1;
+            // a detached prefill joins: its first token is sampled from its last prompt row in this step
+            outr[i] = (s && s->prefilling && join_now && !is_new) ? s->pf_last_row : -1;
         }
     }
     uint32_t row = S, max_pf = 0;
@@ -245,10 +260,11 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         row += P;
         cu[a + 1] = (int32_t)(row - S);
         pfs[a] = s->slot;
-        outr[s->slot] = (int32_t)(row - 1);
+        s->pf_last_row = (int32_t)(row - 1);
+        outr[s->slot] = detach ? -1 : (int32_t)(row - 1);
         if (P > max_pf) max_pf = P;
     }
-    if (!any_decode && admitted.empty()) {
+    if (!any_decode && admitted.empty() && !e->pf_active) {
         int rcf = collect(e);  // nothing to launch: make the last step's tokens visible
         if (rcf) return rcf;
         if (n_running) *n_running = 0;
@@ -259,8 +275,15 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     // 4. launch
     int rc;
     const bool graph = e->cfg.use_cuda_graph != 0;
-    if (graph) rc = r.run_graph(pf_rows, (uint32_t)admitted.size(), max_pf);
-    else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
+    if (detach) {
+        rc = r.launch_prefill_detached(pf_rows, (uint32_t)admitted.size(), max_pf);
+        if (rc) return rc;
+        rc = r.run_graph(0, 0, 0);  // this step's decode rows, beside the prompt
+    } else {
+        if (join_now) { rc = r.join_prefill(); if (rc) return rc; }
+        if (graph) rc = r.run_graph(pf_rows, (uint32_t)admitted.size(), max_pf);
+        else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
+    }
     if (rc) return rc;
     rc = r.mark_done();
     if (rc) return rc;
@@ -270,7 +293,7 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     now.active = true;
     now.bank = r.bank();
     now.any_decode = any_decode;
-    now.has_prefill = pf_rows != 0;
+    now.has_prefill = pf_rows != 0 || r.prefill_in_flight();
     now.attn_bytes = attn_bytes;
     uint32_t running = 0;
     for (uint32_t i = 0; i < S; i++) {
@@ -278,6 +301,11 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         if (!s || s->finished) continue;
         bool is_new = false;
         for (Seq* a : admitted) is_new |= (a == s);
+        if (s->prefilling) {
+            if (is_new || !join_now) { running++; continue; }  // still only a prompt in flight
+            s->prefilling = false;                               // joined: this step sampled its first token
+            is_new = true;
+        }
         s->cached = is_new ? (uint32_t)s->prompt.size() : s->cached + 1;
         now.fill.emplace_back(s, (uint32_t)s->generated.size());
         now.fill_slot.push_back(i);
@@ -286,6 +314,7 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         if (total >= s->max_total) s->finished = true;
         else running++;
     }
+    if (join_now && !detach) e->pf_active = false;
     // the previous step (other bank) has had this step's host work to finish in: read its tokens now
     rc = collect(e);
     if (rc) return rc;

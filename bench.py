@@ -143,6 +143,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--sync-steps", action="store_true", help="read every step's tokens before launching the next one")
+    ap.add_argument("--detached-prefill", action="store_true",
+                    help="prefill an admitted prompt beside the following decode steps instead of inside its admission step")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -177,7 +179,8 @@ def main():
     w = ak.ModelWeights(ctx, cfg, ak.AK_BF16)
     w.init_synthetic(seed=0, std=0.02)  # N(0, 0.02) matrices, N(1, 0.02) gains, generated on the device
     eng = ak.Engine(ctx, w, max_seqs=MAX_SEQS, max_seq_len=TOTAL_LEN, use_cuda_graph=not args.no_graph,
-                    stop_on_eos=False, attn_timing=True, async_steps=not args.sync_steps)
+                    stop_on_eos=False, attn_timing=True, async_steps=not args.sync_steps,
+                    detached_prefill=args.detached_prefill)
     prompts = make_prompts(ak, rank)
     gen_per_job = sum(TOTAL_LEN - len(p) for p in prompts)
     ext = torch.cuda.ExternalStream(ctx.stream, device=local_rank)
@@ -259,7 +262,8 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": WORKLOAD, "l2": "working set per engine step (247 MB weights + ~0.9 GB KV) exceeds the 126 MB L2",
                        "engine_steps_per_job": steps_per_job, "generated_tokens_per_job": gen_per_job,
-                       "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps},
+                       "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps,
+                       "detached_prefill": args.detached_prefill},
             "e2e": {"value": e2e_value, "unit": "tok/s",
                     "h2d_bytes_per_step": (st2["h2d_bytes"] - st["h2d_bytes"]) / args.steps,
                     "d2h_bytes_per_step": (st2["d2h_bytes"] - st["d2h_bytes"]) / args.steps},

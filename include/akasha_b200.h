@@ -338,6 +338,11 @@ typedef struct ak_engine_config {
                                 * Needs stop_on_eos == 0 (sequence ends must be known without the tokens);
                                 * ignored otherwise. poll / block_table / get_stats / clear_finished / run wait for
                                 * the step in flight first. */
+    uint32_t detached_prefill; /* 1: a prompt admitted while other sequences are decoding is prefilled on a second stream,
+                                * beside the following decode-only steps, and joins the batch two steps later (its first
+                                * token is sampled in that step). No other admission until it has joined. Tokens per
+                                * sequence are unchanged; admission times, hence block tables, can differ from the
+                                * default engine. Needs use_cuda_graph; ignored with tensor parallelism. */
 } ak_engine_config;
 
 AK_API int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak_engine** out);
