@@ -92,3 +92,42 @@ def test_synthetic_inputs_are_deterministic(ak):
 def test_error_names(ak):
     e = ak.AkashaError(3, "context window is full (16 tokens)")
     assert e.kind == "ContextFull" and "full" in str(e)
+
+
+def _struct_fields(name):
+    """Member names of `typedef struct <name> { ... } <name>;` in the public header, in order."""
+    text = open(os.path.join(ROOT, "include", "akasha_b200.h")).read()
+    body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (name, name), text, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for decl in body.split(";"):
+        m = re.match(r"\s*(?:uint32_t|uint64_t|float|double|int32_t)\s+(.*)", decl.strip(), re.S)
+        if m:
+            names += [n.strip() for n in m.group(1).split(",")]
+    return names
+
+
+def test_engine_structs_match_the_header(ak):
+    """The ctypes mirrors of the engine's config and statistics structs list the header's members in
+    the header's order (a member added on one side only would shift every later one)."""
+    assert [f for f, _ in ak.EngineConfig._fields_] == _struct_fields("ak_engine_config")
+    assert [f for f, _ in ak.EngineStats._fields_] == _struct_fields("ak_engine_stats")
+    assert C.sizeof(ak.EngineConfig) == 4 * len(ak.EngineConfig._fields_)
+
+
+def test_reference_arm_uses_every_core_under_a_launcher():
+    """`bench.py --impl reference` prints one JSON line from the CPU oracle and does not let a
+    launcher's OMP_NUM_THREADS=1 shrink it to one thread."""
+    import json
+    import subprocess
+    import sys
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, env=env, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "decode tok/s" and d["value"] > 0
+    assert d["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0)) and d["cpu_baseline"]["kind"] == "port"
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
