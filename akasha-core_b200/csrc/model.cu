@@ -229,6 +229,7 @@ Runner::~Runner() {
     if (!ctx_) return;
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
+    if (st2_) cudaStreamSynchronize(st2_);  // a detached prefill may still be running
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     if (ev_desc_) cudaEventDestroy(ev_desc_);
     if (ev_pf_done_) cudaEventDestroy(ev_pf_done_);
