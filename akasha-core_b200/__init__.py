@@ -73,7 +73,9 @@ class EngineStats(C.Structure):
                 ("graph_launches", C.c_uint64), ("eager_steps", C.c_uint64), ("kernel_launches", C.c_uint64),
                 ("attn_ms_total", C.c_double), ("attn_launches_timed", C.c_uint64), ("attn_bytes_total", C.c_uint64),
                 ("h2d_bytes", C.c_uint64), ("d2h_bytes", C.c_uint64),
-                ("step_gpu_ms_total", C.c_double), ("launch_host_ms_total", C.c_double)]
+                ("step_gpu_ms_total", C.c_double), ("launch_host_ms_total", C.c_double),
+                ("decode_step_gpu_ms_total", C.c_double), ("decode_steps_timed", C.c_uint64),
+                ("decode_step_bytes_total", C.c_uint64)]
 
 
 # ------------------------------------------------------------------ library

@@ -3,21 +3,28 @@
 // (src/shaders/cuda.rs:349-419; src/nn/inference_graphs.rs:428-456).
 //
 // Data layout: K pool and V pool are [n_blocks, heads, 16, head_dim]; a (block, head) pair is a
-// contiguous 16 x head_dim tile. One CTA = 4 warps works on one (sequence, head[, split]).
+// contiguous 16 x head_dim tile. One CTA = 4 warps works on one (sequence, head, split): a
+// sequence's KV blocks are divided evenly over up to n_splits CTAs (never fewer than 4 blocks per
+// CTA), so that the longest sequence of a small batch is spread over several SMs.
 // Each warp runs its OWN pipeline over the KV blocks it owns (block index = warp mod 4):
-//   lane 0 issues TMA tiled loads (128-byte swizzle, so the later shared-memory reads are
-//   bank-conflict free) of the K and V tile into a STAGES-deep ring, completion on one mbarrier
-//   per stage; the 32 lanes compute 16 scores (2 lanes per position), run the online softmax
-//   with warp shuffles only, and accumulate P.V with each lane owning head_dim/32 outputs.
-// No CTA-wide barrier sits in the loop; the four warps' (max, sum, acc) are merged once at the
-// end, and with n_splits > 1 the per-split partials are merged by a second small kernel.
+//   TMA tiled loads (128-byte swizzle, so the later shared-memory reads are bank-conflict free) of
+//   the K and V tile into a STAGES-deep ring, completion on one mbarrier per stage; the launcher
+//   picks n_splits so that for a small batch every block of a warp fits the ring and is requested
+//   at once. The online softmax is warp-shuffle only.
+//   bf16 pools: the 16 scores of a tile and P.V go through mma.sync.m16n8k16 (fragments read with
+//   ldmatrix from the swizzled tiles; the query fills every row of the A operand, so the score
+//   accumulators are already laid out as the A operand of P.V): ~80 instructions per warp and tile
+//   where scalar code needs ~500, which is what kept the scalar kernel off the HBM roofline.
+//   f32 pools (parity mode): scalar fp32 FMAs, 2 lanes per position.
+// No CTA-wide barrier sits in the loop; the four warps' (max, sum, acc) are merged once at the end.
+// With more than one split the CTA writes its partial to scratch and bumps an arrival counter; the
+// CTA that arrives last merges the partials in split order (so the sum does not depend on who is
+// last) and clears the counter: one launch, no second kernel, no waiting on other CTAs.
 //
 // Every wait on an mbarrier is bounded; on expiry the kernel records a code in a status word
 // and unwinds.
 #include "kernels.h"
 #include "tma.h"
-
-#include <stdlib.h>
 
 namespace ak {
 
@@ -26,13 +33,15 @@ __device__ unsigned int g_attn_decode_status = 0;
 thread_local bool g_attn_early = false;
 
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_BS = 16;  // positions per KV block
+constexpr int DEC_BS = 16;          // positions per KV block
+constexpr int DEC_MIN_BLOCKS = 4;   // a split never gets fewer KV blocks than this (one per warp)
+constexpr int DEC_MAX_SPLITS = 32;
 
 template <typename T, int HD, int ST> struct DecCfg {
     static constexpr int GROUPS = HD * (int)sizeof(T) / 128;   // 128-byte column groups per row
     static constexpr int EPC = 16 / (int)sizeof(T);            // elements per 16-byte chunk
     static constexpr int EPG = 128 / (int)sizeof(T);           // elements per column group
-    static constexpr int QREGS = GROUPS * 4 * EPC;             // q values held per lane
+    static constexpr int QREGS = GROUPS * 4 * EPC;             // q values held per lane (scalar path)
     static constexpr int EPL = HD / 32;                        // output dims per lane
     static constexpr int TILE_BYTES = DEC_BS * HD * (int)sizeof(T);  // one K (or V) tile
     static constexpr int STAGE_BYTES = 2 * TILE_BYTES;
@@ -40,11 +49,16 @@ template <typename T, int HD, int ST> struct DecCfg {
     static constexpr int SMEM_BYTES = DEC_WARPS * STAGES * STAGE_BYTES + 1024;  // + alignment slack
 };
 
-// exp for the softmax: the accurate routine in the fp32 (parity) instantiation, the fast
-// ex2-based one for bf16 data.
+// exp for the softmax: the accurate routine in the fp32 (parity) instantiation; the bf16 kernel works
+// in the base-2 domain (scores pre-multiplied by log2 e) with the ex2 unit.
 template <typename T> __device__ __forceinline__ float sm_exp(float x) {
     if constexpr (sizeof(T) == 4) return expf(x);
-    else return __expf(x);
+    else return exp2f(x);
+}
+__device__ __forceinline__ float fast_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 template <typename T> __device__ __forceinline__ void unpack16(const uint4& raw, float* out);
@@ -60,6 +74,91 @@ template <> __device__ __forceinline__ void unpack16<bf16>(const uint4& raw, flo
     out[6] = __uint_as_float(raw.w << 16); out[7] = __uint_as_float(raw.w & 0xffff0000u);
 }
 
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8, f32) += A(16x16, bf16, row) * B(16x8, bf16, col)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    bf162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// How a sequence of nblk KV blocks is divided: n_act CTAs (<= n_splits) of bps blocks each, every one
+// of them non-empty. A function of the sequence's own length only.
+__device__ __forceinline__ void split_plan(uint32_t nblk, uint32_t n_splits, uint32_t& n_act, uint32_t& bps) {
+    n_act = (nblk + DEC_MIN_BLOCKS - 1) / DEC_MIN_BLOCKS;
+    if (n_act > n_splits) n_act = n_splits;
+    if (n_act < 1) n_act = 1;
+    bps = (nblk + n_act - 1) / n_act;
+    if (bps) n_act = (nblk + bps - 1) / bps;
+    if (n_act < 1) n_act = 1;
+}
+
+// Scratch layout: [rows*heads*n_splits] partials of (HD + 2) floats (max, sum, acc[HD]), then
+// [rows*heads] arrival counters (uint32, zero between launches).
+__host__ __device__ __forceinline__ size_t partial_floats(uint32_t rows, uint32_t heads, uint32_t hd, uint32_t n_splits) {
+    return (size_t)rows * heads * n_splits * (hd + 2);
+}
+
+// Tail of both kernels, executed by warp 0 with this CTA's merged (M, L, o[EPL] per lane).
+// Single split: normalise and store. Otherwise publish the partial; the last CTA to arrive for this
+// (row, head) merges all n_act partials in split order and clears the counter for the next launch.
+template <typename T, int HD>
+__device__ __forceinline__ void finish_row(float M, float L, float (&o)[HD / 32], T* __restrict__ out, float* __restrict__ scratch,
+                                           uint32_t row, uint32_t h, uint32_t heads, uint32_t rows, uint32_t split, uint32_t n_splits,
+                                           uint32_t n_act, uint32_t lane) {
+    constexpr int EPL = HD / 32;
+    T* orow = out + ((size_t)row * heads + h) * HD + lane * EPL;
+    if (n_act == 1) {
+        const float inv = (L > 0.0f) ? 1.0f / L : 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) orow[e] = Cvt<T>::from_f(o[e] * inv);
+        return;
+    }
+    float* base = scratch + ((size_t)row * heads + h) * n_splits * (HD + 2);
+    float* pr = base + (size_t)split * (HD + 2);
+    if (lane == 0) { pr[0] = M; pr[1] = L; }
+#pragma unroll
+    for (int e = 0; e < EPL; e++) pr[2 + lane * EPL + e] = o[e];
+    __threadfence();
+    __syncwarp();
+    unsigned int* counter = reinterpret_cast<unsigned int*>(scratch + partial_floats(rows, heads, HD, n_splits)) + (size_t)row * heads + h;
+    unsigned int prev = 0;
+    if (lane == 0) prev = atomicAdd(counter, 1u);
+    prev = __shfl_sync(0xffffffffu, prev, 0);
+    if (prev + 1 != n_act) return;
+    __threadfence();
+    float Mx = -INFINITY;
+    for (uint32_t s = 0; s < n_act; s++) Mx = fmaxf(Mx, __ldcg(base + (size_t)s * (HD + 2)));
+    float Ls = 0.0f, acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e++) acc[e] = 0.0f;
+    if (Mx > -INFINITY) {
+        for (uint32_t s = 0; s < n_act; s++) {
+            const float* ps = base + (size_t)s * (HD + 2);
+            const float f = sm_exp<T>(__ldcg(ps) - Mx);
+            Ls += __ldcg(ps + 1) * f;
+#pragma unroll
+            for (int e = 0; e < EPL; e++) acc[e] = fmaf(__ldcg(ps + 2 + lane * EPL + e), f, acc[e]);
+        }
+    }
+    const float inv = (Ls > 0.0f) ? 1.0f / Ls : 0.0f;
+#pragma unroll
+    for (int e = 0; e < EPL; e++) orow[e] = Cvt<T>::from_f(acc[e] * inv);
+    if (lane == 0) *counter = 0u;
+}
+
 template <typename T, int HD, int ST>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -67,12 +166,14 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                          const int32_t* __restrict__ kv_lens, T* __restrict__ out, float* __restrict__ scratch,
                          uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits, uint32_t early) {
     // `early` = the caller guarantees that the kernel launched just before this one wrote nothing of
-    // the cache except each sequence's newest position (the engine's append kernel). Then:
-    // Programmatic dependent launch: the descriptor arrays (lengths, block tables) and every KV
-    // block except the one holding the newest position were written before the preceding kernel
-    // started, so they are fetched BEFORE waiting for it; q and the newest block come after.
+    // the cache except each sequence's newest position (the engine's append kernel), and nothing of the
+    // descriptor arrays. Then, under programmatic dependent launch, the lengths, the block tables and
+    // every KV block except the one holding the newest position are fetched BEFORE waiting for that
+    // kernel; q and the newest block come after. Without `early` nothing is read before the wait.
     pdl_trigger();
+    if (!early) pdl_wait();
     using C = DecCfg<T, HD, ST>;
+    constexpr bool MMA = (sizeof(T) == 2);
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[DEC_WARPS][C::STAGES];
     __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
@@ -81,11 +182,12 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const uint32_t h = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t kv_len = kv_lens[row];
-    const uint32_t dim = heads * HD;
 
     // block range of this split
     const uint32_t nblk = kv_len > 0 ? ((uint32_t)kv_len + DEC_BS - 1) / DEC_BS : 0;
-    const uint32_t bps = (nblk + n_splits - 1) / n_splits;
+    uint32_t n_act, bps;
+    split_plan(nblk, n_splits, n_act, bps);
+    if (split >= n_act) return;   // whole CTA: nothing to do for this (row, head)
     const uint32_t b_begin = split * bps;
     const uint32_t b_end = (b_begin + bps < nblk) ? b_begin + bps : nblk;
 
@@ -99,16 +201,14 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
     __syncwarp();
 
-    const uint32_t p = lane >> 1, hh = lane & 1;
     const int32_t* table = block_tables + (size_t)row * max_blocks;
     // blocks of this warp: b_begin + warp, + DEC_WARPS, ...
     const uint32_t first = b_begin + warp;
     const uint32_t nmine = (first < b_end) ? (b_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
 
-    auto issue = [&](uint32_t i) {  // lane 0 only
-        uint32_t s = i % C::STAGES;
-        uint32_t blk = (uint32_t)table[first + i * DEC_WARPS];
-        int32_t y = (int32_t)((blk * heads + h) * DEC_BS);
+    auto issue = [&](uint32_t i, uint32_t blk) {  // one lane
+        const uint32_t s = i % C::STAGES;
+        const int32_t y = (int32_t)((blk * heads + h) * DEC_BS);
         uint8_t* kdst = my_smem + (size_t)s * C::STAGE_BYTES;
         uint8_t* vdst = kdst + C::TILE_BYTES;
         mbar_expect_tx(&full_bar[warp][s], C::STAGE_BYTES);
@@ -119,24 +219,130 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         }
     };
 
-    // first ring of loads; the block that holds the newest position (written by the preceding
-    // kernel) is held back until that kernel is known to be complete
+    // first ring of loads, one lane per stage (each reads its own block-table entry); the block that
+    // holds the newest position (written by the preceding kernel) is held back until that kernel is
+    // known to be complete
     const uint32_t pre = nmine < (uint32_t)C::STAGES ? nmine : (uint32_t)C::STAGES;
-    uint32_t deferred = 0xffffffffu;
-    if (!early) pdl_wait();
-    if (lane == 0) {
-        for (uint32_t i = 0; i < pre; i++) {
-            if (early && first + i * DEC_WARPS + 1 == nblk) deferred = i;
-            else issue(i);
-        }
+    uint32_t my_blk = 0;
+    bool deferred = false;
+    if (lane < pre) {
+        my_blk = (uint32_t)table[first + lane * DEC_WARPS];
+        deferred = early && (first + lane * DEC_WARPS + 1 == nblk);
+        if (!deferred) issue(lane, my_blk);
     }
-    pdl_wait();
-    if (lane == 0 && deferred != 0xffffffffu) issue(deferred);
+    if (early) pdl_wait();
+    if (deferred) issue(lane, my_blk);
+    __syncwarp();
 
-    // q slice of this lane: position pair-half hh = lane & 1 owns chunks [4hh, 4hh+4) of every group
-    float qreg[C::QREGS];
-    {
-        const T* qrow = q + (size_t)row * dim + (size_t)h * HD;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool failed = false;
+    const T* qrow = q + ((size_t)row * heads + h) * HD;
+
+    if constexpr (MMA) {
+        // ---------------- bf16: tensor-core tiles -------------------------------------------------
+        constexpr int KS = HD / 16;   // k-steps of Q.K^T
+        constexpr int NT = HD / 8;    // 8-wide output tiles of P.V
+        const uint32_t g8 = lane >> 2, t4 = lane & 3;
+        (void)g8;
+        // A operand of Q.K^T: every row is q, so a0 == a1 and a2 == a3
+        uint32_t qa[KS][2];
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+        }
+        // per-lane ldmatrix row addresses inside a tile (swizzled): matrix mi = lane / 8, row r = lane % 8
+        const uint32_t mi = lane >> 3, r8 = lane & 7;
+        // K (no transpose): matrices (pos 0-7, lo dims), (pos 0-7, hi dims), (pos 8-15, lo), (pos 8-15, hi)
+        const uint32_t k_pos = r8 + 8 * (mi >> 1), k_csel = mi & 1;
+        // V (transpose): matrices (pos 0-7, chunk c), (pos 8-15, chunk c), (pos 0-7, chunk c+1), (pos 8-15, chunk c+1)
+        const uint32_t v_pos = r8 + 8 * (mi & 1), v_csel = mi >> 1;
+        float acc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; j++) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f; }
+        const float sl2 = scale * 1.4426950408889634f;   // scores in the base-2 domain
+
+        for (uint32_t i = 0; i < nmine; i++) {
+            const uint32_t s = i % C::STAGES;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[warp][s], (i / C::STAGES) & 1u));
+            if (!ok) { failed = true; break; }
+            const uint32_t ksm = smem_u32(my_smem + (size_t)s * C::STAGE_BYTES);
+            const uint32_t vsm = ksm + C::TILE_BYTES;
+            const uint32_t blk_idx = first + i * DEC_WARPS;
+            const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
+            const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
+            if (n_valid < DEC_BS) {
+                // rows past the end of the sequence may hold anything (their probability is 0, but
+                // 0 * NaN would poison the tensor-core sum): clear them in the V tile
+                uint8_t* vgen = my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES;
+                for (uint32_t c = lane; c < (DEC_BS - n_valid) * 8 * C::GROUPS; c += 32) {
+                    const uint32_t rr = n_valid + c / (8 * C::GROUPS), rem = c % (8 * C::GROUPS);
+                    *reinterpret_cast<uint4*>(vgen + (rem >> 3) * (DEC_BS * 128) + rr * 128 + (rem & 7) * 16) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+            // ---- S = q . K^T : sc[0] = positions 0-7, sc[1] = positions 8-15; this lane's columns 2*t4, 2*t4+1
+            float sc[2][4];
+            sc[0][0] = sc[0][1] = sc[0][2] = sc[0][3] = 0.0f;
+            sc[1][0] = sc[1][1] = sc[1][2] = sc[1][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                const uint32_t grp = (2 * ks) >> 3, chunk = ((2 * ks) & 7) + k_csel;
+                uint32_t kb[4];
+                ldsm_x4(ksm + grp * (DEC_BS * 128) + k_pos * 128 + ((chunk ^ (k_pos & 7)) << 4), kb);
+                mma_bf16_16816(sc[0], qa[ks][0], qa[ks][0], qa[ks][1], qa[ks][1], kb[0], kb[1]);
+                mma_bf16_16816(sc[1], qa[ks][0], qa[ks][0], qa[ks][1], qa[ks][1], kb[2], kb[3]);
+            }
+            float s0 = sc[0][0] * sl2, s1 = sc[0][1] * sl2, s2 = sc[1][0] * sl2, s3 = sc[1][1] * sl2;
+            if (n_valid < DEC_BS) {
+                if (2 * t4 >= n_valid) s0 = -INFINITY;
+                if (2 * t4 + 1 >= n_valid) s1 = -INFINITY;
+                if (8 + 2 * t4 >= n_valid) s2 = -INFINITY;
+                if (9 + 2 * t4 >= n_valid) s3 = -INFINITY;
+            }
+            // ---- online softmax (the 4 lanes of a quad hold the 16 positions; quads are replicas)
+            float mb = fmaxf(fmaxf(s0, s1), fmaxf(s2, s3));
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+            mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+            const float m_new = fmaxf(m_run, mb);
+            const float corr = fast_ex2(m_run - m_new);   // ex2(-inf) = 0 on the first block
+            const uint32_t p01 = pack_bf16x2(fast_ex2(s0 - m_new), fast_ex2(s1 - m_new));
+            const uint32_t p23 = pack_bf16x2(fast_ex2(s2 - m_new), fast_ex2(s3 - m_new));
+            // the row sum adds the bf16-rounded probabilities, the values the tensor core multiplies
+            float lb = __uint_as_float(p01 << 16) + __uint_as_float(p01 & 0xffff0000u) + __uint_as_float(p23 << 16) +
+                       __uint_as_float(p23 & 0xffff0000u);
+            lb += __shfl_xor_sync(0xffffffffu, lb, 1);
+            lb += __shfl_xor_sync(0xffffffffu, lb, 2);
+            l_run = l_run * corr + lb;
+            if (m_new != m_run) {   // warp-uniform
+#pragma unroll
+                for (int j = 0; j < NT; j++) { acc[j][0] *= corr; acc[j][1] *= corr; }
+            }
+            m_run = m_new;
+            // ---- O += P . V
+#pragma unroll
+            for (int jj = 0; jj < NT / 2; jj++) {
+                const uint32_t grp = (2 * jj) >> 3, chunk = ((2 * jj) & 7) + v_csel;
+                uint32_t vb[4];
+                ldsm_x4_trans(vsm + grp * (DEC_BS * 128) + v_pos * 128 + ((chunk ^ (v_pos & 7)) << 4), vb);
+                mma_bf16_16816(acc[2 * jj], p01, p01, p23, p23, vb[0], vb[1]);
+                mma_bf16_16816(acc[2 * jj + 1], p01, p01, p23, p23, vb[2], vb[3]);
+            }
+            __syncwarp();
+            if (i + C::STAGES < nmine && lane == 0) issue(i + C::STAGES, (uint32_t)table[first + (i + C::STAGES) * DEC_WARPS]);
+        }
+        // rows of the accumulator are replicas: quad 0 (lanes 0-3) publishes the warp's output
+        if (lane < 4) {
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                sm_acc[warp][8 * j + 2 * lane] = acc[j][0];
+                sm_acc[warp][8 * j + 2 * lane + 1] = acc[j][1];
+            }
+        }
+    } else {
+        // ---------------- f32 (parity mode): scalar FMAs, 2 lanes per position ---------------------
+        const uint32_t p = lane >> 1, hh = lane & 1;
+        float qreg[C::QREGS];
 #pragma unroll
         for (int g = 0; g < C::GROUPS; g++)
 #pragma unroll
@@ -144,105 +350,91 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 uint4 raw = *reinterpret_cast<const uint4*>(qrow + g * C::EPG + (4 * hh + c) * C::EPC);
                 unpack16<T>(raw, &qreg[(g * 4 + c) * C::EPC]);
             }
-    }
+        float acc[C::EPL];
+#pragma unroll
+        for (int e = 0; e < C::EPL; e++) acc[e] = 0.0f;
 
-    float m_run = -INFINITY, l_run = 0.0f;
-    float acc[C::EPL];
-#pragma unroll
-    for (int e = 0; e < C::EPL; e++) acc[e] = 0.0f;
-    bool failed = false;
+        for (uint32_t i = 0; i < nmine; i++) {
+            const uint32_t s = i % C::STAGES;
+            const bool ok = __all_sync(0xffffffffu, mbar_wait(&full_bar[warp][s], (i / C::STAGES) & 1u));
+            if (!ok) { failed = true; break; }
+            const uint8_t* ksm = my_smem + (size_t)s * C::STAGE_BYTES;
+            const uint8_t* vsm = ksm + C::TILE_BYTES;
+            const uint32_t blk_idx = first + i * DEC_WARPS;
+            const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
+            const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
 
-    for (uint32_t i = 0; i < nmine; i++) {
-        const uint32_t s = i % C::STAGES;
-        if (!mbar_wait(&full_bar[warp][s], (i / C::STAGES) & 1u)) {
-            failed = true;
-            break;
-        }
-        const uint8_t* ksm = my_smem + (size_t)s * C::STAGE_BYTES;
-        const uint8_t* vsm = ksm + C::TILE_BYTES;
-        const uint32_t blk_idx = first + i * DEC_WARPS;
-        const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
-        const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
+            // ---- scores: position p, this lane's half of every 128-byte group
+            float sc = 0.0f;
+#pragma unroll
+            for (int g = 0; g < C::GROUPS; g++)
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    uint32_t chunk = (4 * hh + c) ^ (p & 7);
+                    uint4 raw = *reinterpret_cast<const uint4*>(ksm + g * (DEC_BS * 128) + p * 128 + chunk * 16);
+                    float kf[C::EPC];
+                    unpack16<T>(raw, kf);
+#pragma unroll
+                    for (int e = 0; e < C::EPC; e++) sc = fmaf(qreg[(g * 4 + c) * C::EPC + e], kf[e], sc);
+                }
+            sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+            sc = (p < n_valid) ? sc * scale : -INFINITY;
 
-        // ---- scores: position p, this lane's half of every 128-byte group
-        float sc = 0.0f;
+            // ---- online softmax over the block's 16 positions (lane pairs hold equal values)
+            float mb = sc;
 #pragma unroll
-        for (int g = 0; g < C::GROUPS; g++)
+            for (int o = 16; o > 1; o >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
+            const float m_new = fmaxf(m_run, mb);
+            const float corr = sm_exp<T>(m_run - m_new);
+            const float pj = sm_exp<T>(sc - m_new);  // exp(-inf) = 0 for masked positions
+            float lb = pj;
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-                uint32_t chunk = (4 * hh + c) ^ (p & 7);
-                uint4 raw = *reinterpret_cast<const uint4*>(ksm + g * (DEC_BS * 128) + p * 128 + chunk * 16);
-                float kf[C::EPC];
-                unpack16<T>(raw, kf);
+            for (int o = 16; o > 1; o >>= 1) lb += __shfl_xor_sync(0xffffffffu, lb, o);
+            l_run = l_run * corr + lb;
+            m_run = m_new;
 #pragma unroll
-                for (int e = 0; e < C::EPC; e++) sc = fmaf(qreg[(g * 4 + c) * C::EPC + e], kf[e], sc);
-            }
-        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-        sc = (p < n_valid) ? sc * scale : -INFINITY;
+            for (int e = 0; e < C::EPL; e++) acc[e] *= corr;
 
-        // ---- online softmax over the block's 16 positions (lane pairs hold equal values)
-        float mb = sc;
+            // ---- P.V: lane owns dims [lane*EPL, lane*EPL+EPL)
+            {
+                constexpr int LB = C::EPL * (int)sizeof(T);  // bytes per lane per row (8 or 16)
+                const uint32_t byte_off = lane * LB;
+                const uint32_t g = byte_off >> 7, cin = (byte_off & 127) >> 4, within = byte_off & 15;
+                const uint8_t* vbase = vsm + g * (DEC_BS * 128) + within;
 #pragma unroll
-        for (int o = 16; o > 1; o >>= 1) mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, o));
-        const float m_new = fmaxf(m_run, mb);
-        const float corr = sm_exp<T>(m_run - m_new);
-        const float pj = sm_exp<T>(sc - m_new);  // exp(-inf) = 0 for masked positions
-        float lb = pj;
-#pragma unroll
-        for (int o = 16; o > 1; o >>= 1) lb += __shfl_xor_sync(0xffffffffu, lb, o);
-        l_run = l_run * corr + lb;
-        m_run = m_new;
-#pragma unroll
-        for (int e = 0; e < C::EPL; e++) acc[e] *= corr;
-
-        // ---- P.V: lane owns dims [lane*EPL, lane*EPL+EPL)
-        {
-            constexpr int LB = C::EPL * (int)sizeof(T);  // bytes per lane per row (4, 8 or 16)
-            const uint32_t byte_off = lane * LB;
-            const uint32_t g = byte_off >> 7, cin = (byte_off & 127) >> 4, within = byte_off & 15;
-            const uint8_t* vbase = vsm + g * (DEC_BS * 128) + within;
-#pragma unroll
-            for (int j = 0; j < DEC_BS; j++) {
-                const float pw = __shfl_sync(0xffffffffu, pj, 2 * j);
-                if ((uint32_t)j < n_valid) {
-                    const uint8_t* vp = vbase + j * 128 + ((cin ^ (j & 7)) << 4);
-                    if constexpr (LB == 4) {
-                        uint32_t raw = *reinterpret_cast<const uint32_t*>(vp);
-                        acc[0] = fmaf(pw, __uint_as_float(raw << 16), acc[0]);
-                        acc[1] = fmaf(pw, __uint_as_float(raw & 0xffff0000u), acc[1]);
-                    } else if constexpr (LB == 8 && sizeof(T) == 2) {
-                        uint2 raw = *reinterpret_cast<const uint2*>(vp);
-                        acc[0] = fmaf(pw, __uint_as_float(raw.x << 16), acc[0]);
-                        acc[1] = fmaf(pw, __uint_as_float(raw.x & 0xffff0000u), acc[1]);
-                        acc[2] = fmaf(pw, __uint_as_float(raw.y << 16), acc[2]);
-                        acc[3] = fmaf(pw, __uint_as_float(raw.y & 0xffff0000u), acc[3]);
-                    } else if constexpr (LB == 8) {
-                        float2 v = *reinterpret_cast<const float2*>(vp);
-                        acc[0] = fmaf(pw, v.x, acc[0]);
-                        acc[1] = fmaf(pw, v.y, acc[1]);
-                    } else {
-                        float4 v = *reinterpret_cast<const float4*>(vp);
-                        acc[0] = fmaf(pw, v.x, acc[0]);
-                        acc[1] = fmaf(pw, v.y, acc[1]);
-                        acc[2] = fmaf(pw, v.z, acc[2]);
-                        acc[3] = fmaf(pw, v.w, acc[3]);
+                for (int j = 0; j < DEC_BS; j++) {
+                    const float pw = __shfl_sync(0xffffffffu, pj, 2 * j);
+                    if ((uint32_t)j < n_valid) {
+                        const uint8_t* vp = vbase + j * 128 + ((cin ^ (j & 7)) << 4);
+                        if constexpr (LB == 8) {
+                            float2 v = *reinterpret_cast<const float2*>(vp);
+                            acc[0] = fmaf(pw, v.x, acc[0]);
+                            acc[1] = fmaf(pw, v.y, acc[1]);
+                        } else {
+                            float4 v = *reinterpret_cast<const float4*>(vp);
+                            acc[0] = fmaf(pw, v.x, acc[0]);
+                            acc[1] = fmaf(pw, v.y, acc[1]);
+                            acc[2] = fmaf(pw, v.z, acc[2]);
+                            acc[3] = fmaf(pw, v.w, acc[3]);
+                        }
                     }
                 }
             }
+            __syncwarp();
+            if (i + C::STAGES < nmine && lane == 0) issue(i + C::STAGES, (uint32_t)table[first + (i + C::STAGES) * DEC_WARPS]);
         }
-        __syncwarp();
-        if (lane == 0 && i + C::STAGES < nmine) issue(i + C::STAGES);
+#pragma unroll
+        for (int e = 0; e < C::EPL; e++) sm_acc[warp][lane * C::EPL + e] = acc[e];
     }
-    if (failed) {
+    if (failed) {   // warp-uniform
         if (lane == 0) atomicExch(&g_attn_decode_status, 1u);
         // give the copies still in flight one more bounded chance to land before leaving
         for (uint32_t i2 = 0; i2 < (uint32_t)C::STAGES; i2++) (void)mbar_wait(&full_bar[warp][i2], 0);
+        __syncwarp();
     }
 
     // ---- merge the four warps
     if (lane == 0) { sm_m[warp] = m_run; sm_l[warp] = l_run; }
-#pragma unroll
-    for (int e = 0; e < C::EPL; e++) sm_acc[warp][lane * C::EPL + e] = acc[e];
     __syncthreads();
     if (warp == 0) {
         float M = sm_m[0];
@@ -260,47 +452,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 for (int e = 0; e < C::EPL; e++) o[e] = fmaf(sm_acc[w][lane * C::EPL + e], f, o[e]);
             }
         }
-        if (n_splits == 1) {
-            float inv = (L > 0.0f) ? 1.0f / L : 0.0f;
-            T* orow = out + (size_t)row * dim + (size_t)h * HD + lane * C::EPL;
-#pragma unroll
-            for (int e = 0; e < C::EPL; e++) orow[e] = Cvt<T>::from_f(o[e] * inv);
-        } else {
-            float* pr = scratch + (((size_t)row * heads + h) * n_splits + split) * (HD + 2);
-            if (lane == 0) { pr[0] = M; pr[1] = L; }
-#pragma unroll
-            for (int e = 0; e < C::EPL; e++) pr[2 + lane * C::EPL + e] = o[e];
-        }
+        finish_row<T, HD>(M, L, o, out, scratch, row, h, heads, gridDim.y, split, n_splits, n_act, lane);
     }
-}
-
-// Merge of split partials: grid (heads, rows), one warp.
-template <typename T, int HD>
-__global__ void attn_decode_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, uint32_t heads,
-                                           uint32_t n_splits) {
-    pdl_wait();
-    pdl_trigger();
-    constexpr int EPL = HD / 32;
-    const uint32_t h = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
-    const float* base = scratch + ((size_t)row * heads + h) * n_splits * (HD + 2);
-    float M = -INFINITY;
-    for (uint32_t s = 0; s < n_splits; s++) M = fmaxf(M, base[(size_t)s * (HD + 2)]);
-    float L = 0.0f, o[EPL];
-#pragma unroll
-    for (int e = 0; e < EPL; e++) o[e] = 0.0f;
-    if (M > -INFINITY) {
-        for (uint32_t s = 0; s < n_splits; s++) {
-            const float* pr = base + (size_t)s * (HD + 2);
-            float f = sm_exp<T>(pr[0] - M);
-            L += pr[1] * f;
-#pragma unroll
-            for (int e = 0; e < EPL; e++) o[e] = fmaf(pr[2 + lane * EPL + e], f, o[e]);
-        }
-    }
-    float inv = (L > 0.0f) ? 1.0f / L : 0.0f;
-    T* orow = out + ((size_t)row * heads + h) * HD + lane * EPL;
-#pragma unroll
-    for (int e = 0; e < EPL; e++) orow[e] = Cvt<T>::from_f(o[e] * inv);
 }
 
 // Any head_dim <= 256 (the reference's small test shapes use 4, 8 and 16): one CTA per
@@ -363,66 +516,67 @@ __global__ void attn_decode_generic_kernel(const T* __restrict__ q, const T* __r
 
 size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t n_splits) {
     if (n_splits <= 1) return 0;
-    return (size_t)rows * heads * n_splits * (head_dim + 2) * sizeof(float);
+    return partial_floats(rows, heads, head_dim, n_splits) * sizeof(float) + (size_t)rows * heads * sizeof(unsigned int);
 }
 
-uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t max_kv_len) {
-    // Enough CTAs to fill 148 SMs x 3 resident CTAs, but never less than 4 KV blocks per split.
-    uint64_t items = (uint64_t)rows * heads;
-    if (items == 0) return 1;
-    uint32_t want = (uint32_t)((444 + items - 1) / items);
-    uint32_t cap = max_kv_len / (4 * DEC_BS);
-    if (cap < 1) cap = 1;
-    if (want > cap) want = cap;
-    if (want > 32) want = 32;
+// Launch plan. A large batch (>= 2 waves of one CTA per (sequence, head)) keeps the GPU busy by itself:
+// a 2-deep ring per warp (33 KB per CTA with bf16 head_dim 64, 6 CTAs = 24 warps per SM) and no splitting,
+// which would only add merges. A small batch is bound by its longest sequence: a 4-deep ring while a stage is
+// at most 4 KB, and enough splits that every warp owns at most one ring of blocks, so that a CTA requests all
+// of its K/V at once and a long sequence runs on several SMs.
+#ifndef AK_DEC_SMALL_BATCH_STAGES
+#define AK_DEC_SMALL_BATCH_STAGES 4
+#endif
+static bool small_batch(uint32_t rows, uint32_t heads) { return (uint64_t)rows * heads < 2 * 148 * 6; }
+static uint32_t ring_depth(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype) {
+    const uint32_t stage = 2 * DEC_BS * head_dim * (kv_dtype == AK_F32 ? 4 : 2);
+    return (stage <= 4096 && small_batch(rows, heads)) ? AK_DEC_SMALL_BATCH_STAGES : 2;
+}
+
+uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, uint32_t max_kv_len) {
+    if (rows == 0 || heads == 0 || !small_batch(rows, heads)) return 1;
+    const uint32_t max_blocks = (max_kv_len + DEC_BS - 1) / DEC_BS;
+    const uint32_t per_cta = DEC_WARPS * ring_depth(rows, heads, head_dim, kv_dtype);
+    uint32_t want = (max_blocks + per_cta - 1) / per_cta;
+    if (want > DEC_MAX_SPLITS) want = DEC_MAX_SPLITS;
     return want < 1 ? 1 : want;
 }
 
 template <typename T, int HD, int ST>
 static int launch_fast_st(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
-                       const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
-                       const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
+                          const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                          const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
     using C = DecCfg<T, HD, ST>;
     CUtensorMap tmK, tmV;
     int rc = make_tmap_2d(&tmK, k_pool, sizeof(T), HD, pool_rows, (uint64_t)HD * sizeof(T), C::EPG, DEC_BS, TMA_SWIZZLE_128B);
     if (rc) return rc;
     rc = make_tmap_2d(&tmV, v_pool, sizeof(T), HD, pool_rows, (uint64_t)HD * sizeof(T), C::EPG, DEC_BS, TMA_SWIZZLE_128B);
     if (rc) return rc;
-    static bool attr_set[64] = {};
-    int dev = 0;
-    AK_CUDA(cudaGetDevice(&dev));
-    if (!attr_set[dev & 63]) {
-        AK_CUDA(cudaFuncSetAttribute(attn_decode_paged_kernel<T, HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
-        attr_set[dev & 63] = true;
+    {
+        static bool attr_set[64] = {};
+        int dev = 0;
+        AK_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(device_cache_mutex());
+        if (!attr_set[dev & 63]) {
+            AK_CUDA(cudaFuncSetAttribute(attn_decode_paged_kernel<T, HD, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+            attr_set[dev & 63] = true;
+        }
     }
     dim3 grid(p.heads, p.rows, n_splits);
-    AK_TRY(launch_k(attn_decode_paged_kernel<T, HD, ST>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, 
-        tmK, tmV, (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits, (uint32_t)(g_attn_early ? 1 : 0)));
-    if (n_splits > 1) {
-        dim3 g2(p.heads, p.rows);
-        AK_TRY(launch_k(attn_decode_combine_kernel<T, HD>, dim3(g2), dim3(32), 0, st, NO_CLUSTER, (const float*)scratch, (T*)out, p.heads, n_splits));
-    }
-    return AK_OK;
+    return launch_k(attn_decode_paged_kernel<T, HD, ST>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, tmK, tmV,
+                    (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits,
+                    (uint32_t)(g_attn_early ? 1 : 0));
 }
 
-// Ring depth: a 2-deep ring per warp keeps a CTA at 33 KB (bf16, head_dim 64), so 6 CTAs = 24
-// warps share an SM and a 64-sequence decode batch is resident in ONE wave. More resident warps
-// hide latency better than a deeper ring per warp. AK_ATTN_STAGES overrides (tuning).
 template <typename T, int HD>
 static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                        const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
                        const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
-    constexpr int STAGE_BYTES = 2 * DEC_BS * HD * (int)sizeof(T);
-    constexpr int DEEP = (STAGE_BYTES <= 4096) ? 4 : (STAGE_BYTES <= 8192 ? 3 : 2);
-    static int forced = -1;
-    if (forced < 0) {
-        const char* e = getenv("AK_ATTN_STAGES");
-        forced = e ? atoi(e) : 0;
+    if constexpr (2 * DEC_BS * HD * (int)sizeof(T) <= 4096 && AK_DEC_SMALL_BATCH_STAGES != 2) {
+        if (ring_depth(p.rows, p.heads, HD, p.kv_dtype) != 2)
+            return launch_fast_st<T, HD, AK_DEC_SMALL_BATCH_STAGES>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
     }
-    int want = 2;  // measured: 6 CTAs/SM x 2 stages beats 3 CTAs/SM x 4 stages at 64 and at 1024 sequences
-    if (forced == 2 || forced == DEEP) want = forced;
-    if (want == 2) return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
-    return launch_fast_st<T, HD, DEEP>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
+    return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
 }
 
 // Rows of the 2-D view [n_blocks*heads*16, head_dim] of a pool. With pool_blocks given, a block
@@ -434,7 +588,7 @@ static uint64_t pool_rows_bound(const ak_attn_decode_params& p) {
 
 int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                              const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
-                             const ak_attn_decode_params& p) {
+                             const ak_attn_decode_params& p, bool counters_are_zero) {
     if (p.rows == 0 || p.heads == 0) return AK_OK;
     AK_REQUIRE(p.block_size == DEC_BS, AK_ERR_UNSUPPORTED, "attn_decode_paged: block_size must be 16");
     AK_REQUIRE(p.kv_dtype <= AK_BF16, AK_ERR_INVALID_ARG, "attn_decode_paged: bad kv_dtype");
@@ -456,8 +610,14 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
         }
         return AK_OK;
     }
-    uint32_t n_splits = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.max_blocks_per_seq * DEC_BS);
+    const uint32_t n_splits = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.head_dim, p.kv_dtype, p.max_blocks_per_seq * DEC_BS);
+    AK_REQUIRE(n_splits <= DEC_MAX_SPLITS, AK_ERR_INVALID_ARG, "attn_decode_paged: n_splits must be at most %d", DEC_MAX_SPLITS);
     AK_REQUIRE(n_splits == 1 || scratch, AK_ERR_INVALID_ARG, "attn_decode_paged: scratch required when n_splits > 1");
+    if (n_splits > 1 && !counters_are_zero) {
+        // the arrival counters behind the partials must start at zero (the kernel leaves them at zero)
+        AK_CUDA(cudaMemsetAsync((float*)scratch + partial_floats(p.rows, p.heads, p.head_dim, n_splits), 0,
+                                (size_t)p.rows * p.heads * sizeof(unsigned int), st));
+    }
     const uint64_t rows_bound = pool_rows_bound(p);
     if (p.kv_dtype == AK_F32) {
         if (p.head_dim == 64) return launch_fast<float, 64>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound);
@@ -478,13 +638,13 @@ using namespace ak;
 extern "C" {
 size_t ak_attn_decode_scratch_bytes(const ak_attn_decode_params* p) {
     if (!p) return 0;
-    uint32_t ns = p->n_splits ? p->n_splits : attn_decode_pick_splits(p->rows, p->heads, p->max_blocks_per_seq * DEC_BS);
+    uint32_t ns = p->n_splits ? p->n_splits : attn_decode_pick_splits(p->rows, p->heads, p->head_dim, p->kv_dtype, p->max_blocks_per_seq * DEC_BS);
     return attn_decode_scratch_bytes(p->rows, p->heads, p->head_dim, ns);
 }
 int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool, const void* v_pool, const int32_t* block_tables,
                          const int32_t* kv_lens, void* out, void* scratch, ak_attn_decode_params p) {
     AK_REQUIRE(q && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_paged: null pointer");
-    return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p);
+    return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, false);
 }
 }
 
@@ -510,6 +670,7 @@ static int noalloc_scratch_ptr(void** out) {
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
     AK_REQUIRE(dev >= 0 && dev < 64, AK_ERR_UNSUPPORTED, "attn_decode_paged_noalloc: device index %d not supported", dev);
+    std::lock_guard<std::mutex> lock(device_cache_mutex());
     if (!ptrs[dev]) {
         void* p = nullptr;
         AK_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
@@ -527,18 +688,19 @@ size_t ak_attn_decode_noalloc_max_scratch_bytes(void) { return AK_NOALLOC_SCRATC
 int ak_attn_decode_paged_noalloc(void* stream, const void* q, const void* k_pool, const void* v_pool,
                                  const int32_t* block_tables, const int32_t* kv_lens, void* out, ak_attn_decode_params p) {
     AK_REQUIRE(q && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_paged_noalloc: null pointer");
-    const uint32_t ns = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.max_blocks_per_seq * DEC_BS);
+    const uint32_t ns = p.n_splits ? p.n_splits : attn_decode_pick_splits(p.rows, p.heads, p.head_dim, p.kv_dtype, p.max_blocks_per_seq * DEC_BS);
     const size_t need = attn_decode_scratch_bytes(p.rows, p.heads, p.head_dim, ns);
     AK_REQUIRE(need <= AK_NOALLOC_SCRATCH_BYTES, AK_ERR_UNSUPPORTED,
-               "ak_attn_decode_paged_noalloc: rows*heads*n_splits*(head_dim+2)*4 = %zu bytes of split partials exceed the built-in "
+               "ak_attn_decode_paged_noalloc: %zu bytes of split partials and arrival counters exceed the built-in "
                "%zu-byte buffer; lower n_splits or use ak_attn_decode_paged with caller scratch",
                need, (size_t)AK_NOALLOC_SCRATCH_BYTES);
     void* scratch = nullptr;
     int rc = noalloc_scratch_ptr(&scratch);
     if (rc) return rc;
     p.n_splits = ns;
-    // Every partial the merge kernel reads is written by the split kernel of the same call, so the
-    // buffer's previous contents never matter and nothing has to be cleared.
-    return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p);
+    // Every partial that is read was written earlier in the same call, so the previous call's partials never
+    // matter. The arrival counters behind them must start at zero: the launch clears them on the stream first
+    // (a memset, not an allocation), whatever an earlier, possibly failed, call left there.
+    return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, false);
 }
 }

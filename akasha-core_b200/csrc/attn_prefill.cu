@@ -261,6 +261,7 @@ static int launch_tiled_rpt(cudaStream_t st, const T* q, const T* k, const T* v,
     static bool attr_set[64] = {};
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(device_cache_mutex());
     if (!attr_set[dev & 63]) {
         AK_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<T, HD, PAGED, RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[dev & 63] = true;
@@ -304,8 +305,7 @@ int launch_attn_prefill_paged(cudaStream_t st, const void* q, const void* k_pool
     if (n_seqs == 0 || max_len == 0) return AK_OK;
     AK_REQUIRE(block_size == PF_BS, AK_ERR_UNSUPPORTED, "prefill attention: block_size must be 16");
     // bf16 with a tensor-core friendly head size: the tcgen05 kernel (needs the extents for its tensor maps)
-    static const bool tc_on = [] { const char* e = getenv("AK_PREFILL_TC"); return !(e && e[0] == '0'); }();
-    if (tc_on && dtype == AK_BF16 && (head_dim == 64 || head_dim == 128) && q_rows && pool_blocks)
+    if (dtype == AK_BF16 && (head_dim == 64 || head_dim == 128) && q_rows && pool_blocks)
         return launch_attn_prefill_tc(st, q, q_rows, k_pool, v_pool, pool_blocks, block_tables, max_blocks_per_seq, cu, seq_slot, out,
                                       n_seqs, max_len, row_base, heads, head_dim, scale);
     if (dtype == AK_F32) {

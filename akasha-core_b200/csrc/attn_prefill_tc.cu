@@ -100,14 +100,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                   uint32_t heads, float scale) {
     using C = Cfg<HD, BKV>;
     pdl_wait();
-    pdl_trigger();
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_bar, kv_bar[2], s_bar, pv_bar;
     __shared__ uint32_t tmem_base_sm, fail_flag;
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BQ;
     const uint32_t len = (uint32_t)(cu[seq + 1] - cu[seq]);
-    if (q0 >= len) return;
+    if (q0 >= len) { pdl_trigger(); return; }   // allocates no TMEM
     const uint32_t row0 = row_base + (uint32_t)cu[seq];
     const int32_t* table = block_tables + (size_t)seq_slot[seq] * max_blocks;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -127,6 +126,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Invariant of every TMEM-using kernel of this library: dependents are released only AFTER this CTA holds its
+    // TMEM columns. A dependent grid's CTAs allocate TMEM and then block in griddepcontrol.wait until this grid
+    // has completed; were they let in first, they could take the columns this CTA still needs and both would wait.
+    pdl_trigger();
     const uint32_t tmem_s = tmem_base_sm, tmem_pv = tmem_base_sm + BKV;
     const uint32_t lane_addr = (warp * 32u) << 16;
 
@@ -312,6 +315,7 @@ static int launch(cudaStream_t st, const void* q, uint64_t q_rows, const void* k
     static bool attr_set[64] = {};
     int dev = 0;
     AK_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(device_cache_mutex());
     if (!attr_set[dev & 63]) {
         AK_CUDA(cudaFuncSetAttribute(prefill_tc_kernel<HD, BKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         attr_set[dev & 63] = true;
@@ -329,12 +333,11 @@ int launch_attn_prefill_tc(cudaStream_t st, const void* q, uint64_t q_rows, cons
     if (n_seqs == 0 || max_len == 0) return AK_OK;
     const uint64_t pool_rows = pool_blocks * heads * pftc::BS;
     // keys per step: 128 for head_dim 64 (a little faster); 64 for head_dim 128, where 128 would leave room for
-    // one CTA per SM only (measured slower on long prompts). AK_PREFILL_BKV=64|128 forces one, for comparison.
-    static const int forced = [] { const char* e = getenv("AK_PREFILL_BKV"); return e ? atoi(e) : 0; }();
+    // one CTA per SM only (measured slower on long prompts).
 #define AK_PF_ARGS st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, row_base, heads, scale
-    if (head_dim == 64) return forced == 64 ? pftc::launch<64, 64>(AK_PF_ARGS) : pftc::launch<64, 128>(AK_PF_ARGS);
+    if (head_dim == 64) return pftc::launch<64, 128>(AK_PF_ARGS);
     AK_REQUIRE(head_dim == 128, AK_ERR_UNSUPPORTED, "prefill attention (tensor cores): head_dim must be 64 or 128");
-    return forced == 128 ? pftc::launch<128, 128>(AK_PF_ARGS) : pftc::launch<128, 64>(AK_PF_ARGS);
+    return pftc::launch<128, 64>(AK_PF_ARGS);
 #undef AK_PF_ARGS
 }
 

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/akasha_b200.h"
 
 namespace ak {
@@ -46,6 +48,10 @@ static inline size_t cdiv64(size_t a, size_t b) { return (a + b - 1) / b; }
 // after, which lets the NEXT kernel's blocks be scheduled early and run their prologue while this
 // grid drains. Without the launch attribute both instructions are no-ops.
 bool pdl_enabled();
+
+// One mutex for the small per-device caches kept in function-local statics (kernel attributes already set,
+// symbol addresses already looked up): the library may be driven from one host thread per GPU.
+std::mutex& device_cache_mutex();
 
 // Number of kernel launches issued by this library on the calling thread (for the benchmark's
 // `gpu_launches` claim).

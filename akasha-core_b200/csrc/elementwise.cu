@@ -115,17 +115,25 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
     ss = warp_sum(ss);
     float rs = 1.0f / sqrtf((ss / (float)size) + eps);
     float pos = ROPE ? (float)positions[warp] : 0.0f;
+    // RoPE factors of the two pairs (d0, d0+1), (d0+2, d0+3) of a float4. A lane visits float4 indices
+    // lane, lane + 32, ...: 128 elements apart, so when head_dim divides 128 every one of them sits at the same
+    // offset d0 inside its head and the transcendental work is done once per lane and row, not once per float4.
+    const bool same_d0 = ROPE && (128u % head_dim) == 0;
+    float hs0 = 0.f, hc0 = 1.f, hs1 = 0.f, hc1 = 1.f;
+    auto factors = [&](uint32_t d0, float& s0, float& c0, float& s1, float& c1) {
+        float f0 = 1.0f / powf(10000.0f, (float)d0 / (float)head_dim);
+        float f1 = 1.0f / powf(10000.0f, (float)(d0 + 2) / (float)head_dim);
+        sincosf(pos * f0, &s0, &c0);
+        sincosf(pos * f1, &s1, &c1);
+    };
+    if (same_d0) factors((lane * 4) % head_dim, hs0, hc0, hs1, hc1);
 
     auto emit4 = [&](uint32_t i4, float4 v) {
         float4 g = reinterpret_cast<const float4*>(w)[i4];
         float o0 = v.x * rs * g.x, o1 = v.y * rs * g.y, o2 = v.z * rs * g.z, o3 = v.w * rs * g.w;
         if (ROPE) {
-            uint32_t d0 = (i4 * 4) % head_dim;  // even, pairs (d0,d0+1) and (d0+2,d0+3)
-            float f0 = 1.0f / powf(10000.0f, (float)d0 / (float)head_dim);
-            float f1 = 1.0f / powf(10000.0f, (float)(d0 + 2) / (float)head_dim);
-            float s0, c0, s1, c1;
-            sincosf(pos * f0, &s0, &c0);
-            sincosf(pos * f1, &s1, &c1);
+            float s0 = hs0, c0 = hc0, s1 = hs1, c1 = hc1;
+            if (!same_d0) factors((i4 * 4) % head_dim, s0, c0, s1, c1);  // even d0, pairs (d0,d0+1) and (d0+2,d0+3)
             float a = o0 * c0 - o1 * s0, b = o0 * s0 + o1 * c0;
             float c = o2 * c1 - o3 * s1, d = o2 * s1 + o3 * c1;
             o0 = a; o1 = b; o2 = c; o3 = d;
@@ -375,7 +383,9 @@ int launch_rope_kv_append(cudaStream_t st, const float* qkv, const int32_t* posi
                           uint32_t rope_table_len, uint32_t tokens, uint32_t heads, uint32_t head_dim,
                           uint32_t block_size, uint32_t kv_dtype) {
     if (tokens == 0) return AK_OK;
-    AK_REQUIRE(head_dim % 8 == 0, AK_ERR_UNSUPPORTED, "rope_kv_append: head_dim must be a multiple of 8");
+    // the kernels work on 16-byte chunks of the output: 4 f32 or 8 bf16 elements
+    AK_REQUIRE(head_dim % (kv_dtype == AK_F32 ? 4 : 8) == 0, AK_ERR_UNSUPPORTED, "rope_kv_append: head_dim must be a multiple of %d for this dtype",
+               kv_dtype == AK_F32 ? 4 : 8);
     if (kv_dtype == AK_F32) {
         size_t total = (size_t)tokens * heads * (head_dim / 4);
         AK_TRY(launch_k(rope_kv_append_kernel<float>, dim3((unsigned)cdiv64(total, 256)), dim3(256), 0, st, NO_CLUSTER, 

@@ -46,6 +46,7 @@ struct ak_engine {
     uint64_t next_id = 1;
     ak_engine_stats stats{};
     unsigned long long launch_base = 0;
+    double launch_host_base = 0.0;   // the runner's cumulative launch time at the last ak_engine_reset_stats
     // a step that has been launched and whose tokens have not been read yet
     struct Pending {
         bool active = false;
@@ -55,7 +56,9 @@ struct ak_engine {
         bool any_decode = false;
         bool has_prefill = false;
         uint64_t attn_bytes = 0;
+        uint64_t step_bytes = 0;
     } pending;
+    uint64_t weight_bytes = 0;   // bytes of every tensor a decode step reads in full (all but the embedding table)
     uint64_t step_index = 0;
     bool pf_active = false;      // a detached prefill has been launched and has not joined yet
     uint64_t pf_join_step = 0;   // the step in which its sequences sample their first token
@@ -79,9 +82,15 @@ static int collect(ak_engine* e) {
         s->generated[p.fill[i].second] = tok;
         if (e->cfg.stop_on_eos && tok == mc.eos_token) s->finished = true;
     }
-    if (e->cfg.attn_timing) e->stats.step_gpu_ms_total += r.last_step_gpu_ms();
+    const float step_ms = e->cfg.attn_timing ? r.last_step_gpu_ms() : 0.0f;
+    e->stats.step_gpu_ms_total += step_ms;
     // the roofline sample: decode-only steps (in an admission step the prompt's kernels run beside the attention)
     if (e->cfg.attn_timing && p.any_decode && !p.has_prefill) {
+        if (step_ms > 0.0f) {
+            e->stats.decode_step_gpu_ms_total += step_ms;
+            e->stats.decode_steps_timed++;
+            e->stats.decode_step_bytes_total += p.step_bytes;
+        }
         float ms = r.last_attn_ms();
         if (ms > 0.0f) {
             e->stats.attn_ms_total += ms;
@@ -128,6 +137,8 @@ int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak
     }
     e->runner.enable_attn_timing(cfg->attn_timing != 0);
     e->runner.set_keep_logits(false);
+    for (const auto& pr : w->params)
+        if (pr.kind != 1) e->weight_bytes += pr.llen * (pr.kind == 0 ? 4 : (w->dtype == AK_F32 ? 4 : 2));
     for (uint32_t b = 0; b < e->cfg.kv_blocks; b++) e->free_blocks.insert((int32_t)b);
     e->slots.assign(cfg->max_seqs, nullptr);
     *out = e;
@@ -150,6 +161,9 @@ int ak_engine_submit(ak_engine* e, const uint32_t* prompt, uint32_t n, uint32_t 
                "prompt is %u tokens, context window is %u (step budget %u)", n, e->cfg.max_seq_len, e->runner.max_prefill_tokens());
     if (max_total_len > e->cfg.max_seq_len) max_total_len = e->cfg.max_seq_len;
     AK_REQUIRE(max_total_len > n, AK_CONTEXT_FULL, "context window is full (%u tokens)", max_total_len);
+    // a sequence reserves all of its blocks at admission: one that needs more than the pool holds could never start
+    AK_REQUIRE((max_total_len + 15) / 16 <= e->cfg.kv_blocks, AK_CONTEXT_FULL,
+               "sequence of up to %u tokens needs %u KV blocks, the pool holds %u", max_total_len, (max_total_len + 15) / 16, e->cfg.kv_blocks);
     Seq* s = new Seq();
     s->id = e->next_id++;
     s->prompt.assign(prompt, prompt + n);
@@ -295,6 +309,10 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     now.any_decode = any_decode;
     now.has_prefill = pf_rows != 0 || r.prefill_in_flight();
     now.attn_bytes = attn_bytes;
+    // per layer: the attention launch's bytes plus one appended K and V row per sequence; per step: the weights
+    // and one embedding row per sequence
+    now.step_bytes = e->weight_bytes + (uint64_t)n_dec * mc.dim * esz +
+                     (uint64_t)mc.num_layers * (attn_bytes + (uint64_t)n_dec * 2 * r.local_qdim() * esz);
     uint32_t running = 0;
     for (uint32_t i = 0; i < S; i++) {
         Seq* s = e->slots[i];
@@ -333,7 +351,7 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     if (graph) e->stats.graph_launches++; else e->stats.eager_steps++;
     e->stats.kernel_launches += (g_launch_count - launches0);
     e->stats.h2d_bytes = r.h2d_bytes;
-    e->stats.launch_host_ms_total = r.launch_host_ms;
+    e->stats.launch_host_ms_total = r.launch_host_ms - e->launch_host_base;
     e->stats.d2h_bytes = r.d2h_bytes;
     (void)mc;
     if (n_running) *n_running = running;
@@ -347,10 +365,14 @@ int ak_engine_run(ak_engine* e, uint64_t max_steps, uint64_t* steps_done) {
     for (;;) {
         if (max_steps && n >= max_steps) break;
         uint32_t running = 0, waiting = 0;
+        const uint64_t launched0 = e->stats.steps;
         int rc = ak_engine_step(e, &running, &waiting);
         if (rc) return rc;
         n++;
         if (running == 0 && waiting == 0) break;
+        // nothing runs, nothing was launched, yet sequences wait: no later step can admit them either
+        AK_REQUIRE(!(running == 0 && e->stats.steps == launched0 && !e->pf_active), AK_ERR_INVALID_ARG,
+                   "ak_engine_run: %u waiting sequence(s) can never be admitted (KV pool or step budget too small)", waiting);
     }
     int rc = collect(e);
     if (rc) return rc;
@@ -409,7 +431,9 @@ int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out) {
 }
 int ak_engine_reset_stats(ak_engine* e) {
     AK_REQUIRE(e, AK_ERR_INVALID_ARG, "ak_engine_reset_stats: null engine");
+    { int rcf = collect(e); if (rcf) return rcf; }
     e->stats = ak_engine_stats{};
+    e->launch_host_base = e->runner.launch_host_ms;
     return AK_OK;
 }
 

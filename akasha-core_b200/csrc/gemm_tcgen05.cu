@@ -469,8 +469,7 @@ static constexpr uint32_t SMEM_ONE_PER_SM = 220 * 1024;
 // Rows of the activation TMA box: a decode batch fills only part of the 128-row MMA tile, and rows the
 // box does not fetch cost neither L2 requests nor zero-fill writes.
 static uint32_t a_box_rows(uint32_t m) {
-    static const bool full = [] { const char* e = getenv("AK_GEMM_FULLBOX"); return e && e[0] == '1'; }();
-    if (full || m > 64) return GB_M;
+    if (m > 64) return GB_M;
     return m > 32 ? 64 : (m > 16 ? 32 : 16);
 }
 static uint32_t stage_bytes(uint32_t bn) { return GB_M * GB_K * 2 + bn * GB_K * 2; }
@@ -526,15 +525,6 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         p.ks = 1;
         // Two CTAs per SM (one's epilogue under the other's main loop) beat one CTA with a deeper ring.
         uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
-        if (const char* e = getenv("AK_GEMM_BIGPLAN")) {  // tuning aid: "bn,stages" for the large-m plan
-            unsigned b = 0, t = 0;
-            if (sscanf(e, "%u,%u", &b, &t) == 2 && (b == 256 || b == 128 || b == 64 || b == 32) && t >= 1) {
-                p.bn = b;
-                st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
-                if (t < st) st = t;
-                if (st < 1) st = 1;
-            }
-        }
         if (st > G_MAX_STAGES) st = G_MAX_STAGES;
         if (p.bn <= 64 && st > 6) st = 6;
         p.stages = st < num_kb ? st : (num_kb ? num_kb : 1);
@@ -575,18 +565,9 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             const bool better = per < best_kb || (per == best_kb && ctas > best_ctas);
             if (better) { best_kb = per; best_ctas = ctas; p.bn = bn; p.ks = ks; }
         }
-    uint32_t force_st = 0;
-    if (const char* e = getenv("AK_GEMM_PLAN")) {  // tuning aid: "bn,ks,stages" for the skinny plan
-        unsigned b = 0, s2 = 0, t = 0;
-        if (sscanf(e, "%u,%u,%u", &b, &s2, &t) == 3 && (b == 16 || b == 32 || b == 64) && (s2 == 1 || s2 == 2 || s2 == 4 || s2 == 8) &&
-            (s2 == 1 || (allow_split && (b / s2) % 4 == 0 && s2 * 2 <= num_kb))) {
-            p.bn = b; p.ks = s2; force_st = t;
-        }
-    }
     const uint32_t per = cdiv(num_kb, p.ks);
     const uint32_t red = p.ks > 1 ? GB_M * p.bn * 4 : 0;
     uint32_t st = (SMEM_TWO_PER_SM - 1024 - red) / stage_bytes(p.bn);
-    if (force_st && force_st < st) st = force_st;
     if (st > G_MAX_STAGES) st = G_MAX_STAGES;
     if (st < 2) st = 2;
     p.stages = st < per ? st : (per ? per : 1);
@@ -598,13 +579,17 @@ static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap
                       uint32_t k, const GemmPlan& p) {
     using C = GemmCfg<BN>;
     const size_t smem = (size_t)p.stages * C::STAGE_BYTES + (p.ks > 1 ? C::RED_BYTES : 0) + 1024;
-    static size_t attr_set[64] = {};
-    int dev = 0;
-    AK_CUDA(cudaGetDevice(&dev));
-    if (attr_set[dev & 63] < smem) {
-        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
-        AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
-        attr_set[dev & 63] = SMEM_ONE_PER_SM;
+    {
+        // per-device "attribute set" flags; the library may be driven from one host thread per GPU
+        static size_t attr_set[64] = {};
+        int dev = 0;
+        AK_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(device_cache_mutex());
+        if (attr_set[dev & 63] < smem) {
+            AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+            AK_CUDA(cudaFuncSetAttribute(gemm_bf16_kernel<BN, EPI, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+            attr_set[dev & 63] = SMEM_ONE_PER_SM;
+        }
     }
     uint32_t need = p.kseg * BN, cols = 32;
     while (cols < need) cols *= 2;

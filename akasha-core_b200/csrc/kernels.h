@@ -70,10 +70,12 @@ int launch_argmax_finish(cudaStream_t st, const float* part_val, const uint32_t*
 
 // ---- attn_decode.cu ----------------------------------------------------------------------------
 size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t n_splits);
-uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t max_kv_len);
+uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, uint32_t max_kv_len);
+// scratch (n_splits > 1): partials followed by one arrival counter per (row, head). The counters must be zero
+// when the kernel starts and are zero again when it ends; counters_are_zero = false clears them on the stream first.
 int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                              const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
-                             const ak_attn_decode_params& p);
+                             const ak_attn_decode_params& p, bool counters_are_zero);
 
 int attn_decode_status(unsigned int* out);  // device status word of the decode kernel
 extern thread_local bool g_attn_early;      // true while the runner launches (cache untouched but for the newest positions)

@@ -334,6 +334,7 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaMemsetAsync(logits_, 0, (size_t)max_seqs * logits_ld_ * 4, ctx->stream));
     attn_scratch_bytes_ = attn_decode_scratch_bytes(max_seqs, heads_l_, hd, 32);
     AK_CUDA(cudaMalloc((void**)&attn_scratch_, attn_scratch_bytes_));
+    AK_CUDA(cudaMemsetAsync(attn_scratch_, 0, attn_scratch_bytes_, ctx->stream));   // arrival counters start at zero
 
     // RoPE factors from the host libm, exactly as the reference's CPU kernel forms them
     // (src/shaders/cpu.rs:98-100): freq = 1/powf(10000, d/hd), angle = (float)pos * freq.
@@ -360,10 +361,6 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
     AK_CUDA(cudaEventCreateWithFlags(&ev_desc_, cudaEventDisableTiming));
     AK_CUDA(cudaEventCreateWithFlags(&ev_pf_done_, cudaEventDisableTiming));
-    {
-        const char* e = getenv("AK_TWO_STREAMS");
-        two_streams_ = !(e && e[0] == '0');
-    }
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -434,7 +431,7 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                         else AK_CUDA(cudaEventRecord(ev_attn0_, s));
                     }
                     g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
-                    rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
+                    rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
                     g_attn_early = false;
                     if (rc) return rc;
                     if (timed) {
@@ -489,7 +486,7 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                     else AK_CUDA(cudaEventRecord(ev_attn0_, st));
                 }
                 g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
-                rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p);
+                rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
                 g_attn_early = false;
                 if (rc) return rc;
                 if (timed) {
@@ -546,7 +543,7 @@ int Runner::run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len
     // One split count per runner (from the longest sequence it can hold): eager and captured
     // steps then sum in the same order, so a sequence's tokens do not depend on its neighbours.
     (void)max_kv_len;
-    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
+    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, max_seq_len_);
     int rc = launch_layers(T, n_prefill_rows, n_pf_seqs, max_pf_len, any_decode, n_splits, false);
     if (rc) return rc;
     AK_CUDA(cudaMemcpyAsync(h_sampled_, d_sampled_, (size_t)max_seqs_ * 4, cudaMemcpyDeviceToHost, st));
@@ -594,7 +591,7 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
     const uint64_t key = ((uint64_t)bank_ << 63) | ((uint64_t)rows_b << 32) | seqs_b;  // a graph bakes its bank's host buffers and events
     const uint32_t T = max_seqs_ + rows_b;
     const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
-    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
+    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, max_seq_len_);
     auto it = graphs_.find(key);
     if (it == graphs_.end()) {
         // one eager pass first (sets kernel attributes, surfaces faults outside capture); it IS this step
@@ -684,7 +681,7 @@ int Runner::launch_prefill_detached(uint32_t n_prefill_rows, uint32_t n_pf_seqs,
     pf_slot_saved_.assign(pfs, pfs + seqs_b);
     const uint32_t T = max_seqs_ + rows_b;
     const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
-    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, w_->cfg.num_heads, max_seq_len_);
+    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, max_seq_len_);
     // main stream: the whole descriptor (header + decode rows + prompt rows); the prompt graph starts after it
     AK_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st));
     h2d_bytes += bytes;

@@ -181,7 +181,7 @@ class Runner {
     } banks_[2];
     uint32_t bank_ = 0;
     // Admission steps: the admitted prompts' rows run on a second stream, concurrently with the decode
-    // rows (different sequences: they share nothing until the final norm). AK_TWO_STREAMS=0 keeps one stream.
+    // rows (different sequences: they share nothing until the final norm).
     cudaStream_t st2_ = nullptr;
     cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
     bool two_streams_ = true;

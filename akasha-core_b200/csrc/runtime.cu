@@ -22,6 +22,11 @@ bool pdl_enabled() {
     return v != 0;
 }
 
+std::mutex& device_cache_mutex() {
+    static std::mutex mu;
+    return mu;
+}
+
 void set_error(const char* fmt, ...) {
     va_list ap;
     va_start(ap, fmt);

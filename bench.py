@@ -12,7 +12,11 @@ data-path collective); value is the aggregate over ranks.
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 `--impl reference` times the CPU restatement of the reference's own path (the oracle, all host
-threads) on a bounded sample of the same workload.
+threads) on a bounded sample of the same workload: each step runs ONE sequence of the workload in
+full (prefill of its prompt, then greedy decode to length 512), a different sequence every step,
+so the prompt : generated mix of the sample follows the workload's.
+`--cpu-config1` prints the reference CPU path's own configuration instead (batch 1, prompt of 64
+ids from seed 1, 128 greedy decode steps): prefill ms and decode tok/s, single-thread and all threads.
 """
 from __future__ import annotations
 
@@ -97,41 +101,73 @@ def measured_peak_hbm():
     return 6650.0, "fallback"
 
 
-def cpu_reference_arm(ak, steps: int, warmup: int, sample_seqs: int = 2, decode_steps: int = 48):
-    """The reference's CPU path (restated by the oracle) on a bounded sample: the first
-    `sample_seqs` sequences of the workload, each prefilled and decoded `decode_steps` tokens,
-    one after the other (the reference has no batching), fp32, all host threads."""
+def workload_config(ak):
+    """The `config` object of the JSON line: the same for both arms."""
+    gen = sum(TOTAL_LEN - len(p) for p in make_prompts(ak, 0))
+    return {"workload": WORKLOAD, "generated_tokens_per_step": gen,
+            "l2": "working set per engine step (247 MB weights + ~0.9 GB KV) exceeds the 126 MB L2"}
+
+
+def cpu_reference_arm(ak, steps: int, warmup: int):
+    """The reference's CPU path (restated by the oracle), fp32, all host threads, on a bounded sample
+    of the workload: one step = one sequence of the workload run in full (prefill of its prompt, then
+    greedy decode until its length is 512), sequences taken in workload order, one after the other
+    (the reference has no batching). Over a handful of steps the prompt : generated mix follows the
+    workload's (prompts are uniform in [16, 448])."""
     orc = entry.load_oracle()
     cfg = ak.ModelConfig.akasha_hall_1()
     params = ak.synthetic_weights(cfg, seed=0, std=0.02)
     model = orc.Model(cfg.as_dict(), params)
-    prompts = make_prompts(ak, 0)[:sample_seqs]
+    prompts = make_prompts(ak, 0)
     # every core this process may run on (a launcher may have exported OMP_NUM_THREADS=1: the oracle's own
     # maximum would then read 1)
     cores = max(orc.max_threads(), len(os.sched_getaffinity(0)))
     orc.set_threads(cores)
 
-    def one_pass():
-        gen = 0
+    def one_seq(i):
+        p = prompts[i % len(prompts)]
         t0 = time.perf_counter()
-        for p in prompts:
-            s = orc.Session(model, TOTAL_LEN)
-            st, toks, _ = s.generate_greedy(p, decode_steps)
-            gen += len(toks)
-        return gen, time.perf_counter() - t0
+        s = orc.Session(model, TOTAL_LEN)
+        st, toks, _ = s.generate_greedy(p, TOTAL_LEN - len(p))
+        return len(p), len(toks), time.perf_counter() - t0
 
-    for _ in range(min(warmup, 1)):
-        one_pass()
-    times, gen = [], 0
-    for _ in range(steps):
-        g, t = one_pass()
+    for i in range(warmup):
+        one_seq(steps + i)
+    n_prompt = gen = 0
+    total = 0.0
+    for i in range(steps):
+        pl, g, t = one_seq(i)
+        n_prompt += pl
         gen += g
-        times.append(t)
-    total = sum(times)
-    sample = (f"first {sample_seqs} sequences of the workload (prompt lens {[len(p) for p in prompts]}), prefill + "
-              f"{decode_steps} greedy decode steps each, sequential, fp32 oracle, {cores} OpenMP threads")
+        total += t
+    sample = (f"{steps} of the workload's 256 sequences, each run in full (prompt prefill + greedy decode to length 512; "
+              f"{n_prompt} prompt tokens, {gen} generated), one after the other, fp32 oracle, {cores} OpenMP threads")
     return {"value": gen / total, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample,
             "ms_per_step": 1e3 * total / steps}
+
+
+def cpu_config1(ak):
+    """The reference CPU backend's own configuration: 162M fp32, batch 1, prompt = 64 ids (seed 1), prefill then
+    128 greedy decode steps; timed single-thread (the reference's CPU kernels are scalar loops) and on all threads."""
+    orc = entry.load_oracle()
+    cfg = ak.ModelConfig.akasha_hall_1()
+    model = orc.Model(cfg.as_dict(), ak.synthetic_weights(cfg, seed=0, std=0.02))
+    prompt = ak.uniform_tokens(64, cfg.vocab_size, seed=1)
+    cores = max(orc.max_threads(), len(os.sched_getaffinity(0)))
+    out = {"config": "akasha-hall 162M fp32, batch 1, prompt 64 ids (seed 1), 128 greedy decode steps, CPU oracle"}
+    for name, th in (("single_thread", 1), ("all_threads", cores)):
+        orc.set_threads(th)
+        s = orc.Session(model, TOTAL_LEN)
+        t0 = time.perf_counter()
+        rc, logits = s.prefill(prompt)
+        t1 = time.perf_counter()
+        tok = int(np.argmax(logits))
+        for _ in range(128):
+            rc, logits = s.decode_step(tok)
+            tok = int(np.argmax(logits))
+        t2 = time.perf_counter()
+        out[name] = {"threads": th, "prefill_ms": 1e3 * (t1 - t0), "decode_tok_s": 128 / (t2 - t1)}
+    return out
 
 
 def main():
@@ -141,6 +177,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-config1", action="store_true", help="print the reference CPU configuration's numbers and exit")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--sync-steps", action="store_true", help="read every step's tokens before launching the next one")
     ap.add_argument("--detached-prefill", action="store_true",
@@ -152,15 +189,18 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     ak = entry.load_package()
 
+    if args.cpu_config1:
+        if rank == 0:
+            print(json.dumps(cpu_config1(ak)))
+        return 0
     if args.impl == "reference":
         if rank != 0:
             return 0
-        steps = max(1, min(args.steps, 3))
-        r = cpu_reference_arm(ak, steps, args.warmup)
+        r = cpu_reference_arm(ak, max(1, args.steps), max(0, args.warmup))
         line = {"impl": "reference", "metric": "decode tok/s", "value": r["value"], "unit": "tok/s", "n_gpus": args.gpus,
-                "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                "steps": max(1, args.steps), "warmup": max(0, args.warmup), "ms_per_step": r["ms_per_step"], "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-                "config": {"workload": WORKLOAD},
+                "config": workload_config(ak),
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -185,18 +225,22 @@ def main():
     gen_per_job = sum(TOTAL_LEN - len(p) for p in prompts)
     ext = torch.cuda.ExternalStream(ctx.stream, device=local_rank)
 
+    CHECK = (0, 63, 64, 150, N_SEQS - 1)   # sequences whose ids the two timed legs must agree on
+
     def job(collect: bool):
         """One pass through the public API: submit (host prompts), step until done, poll outputs."""
         ids = [eng.submit(p, TOTAL_LEN) for p in prompts]
         eng.run_to_completion()
-        n = 0
+        n, kept = 0, {}
         if collect:
-            for i in ids:
+            for k, i in enumerate(ids):
                 t, fin = eng.poll(i, TOTAL_LEN)
                 assert fin
                 n += len(t)
+                if k in CHECK:
+                    kept[k] = t
         eng.clear_finished()
-        return n
+        return n, kept
 
     def barrier():
         if world > 1:
@@ -205,6 +249,7 @@ def main():
 
     for _ in range(max(args.warmup, 0)):
         job(False)
+    leg1_ids = {}
     ctx.check_device_status()
 
     # ---- leg 1: device-timed (CUDA events on the engine's stream), prompts queued before the timer
@@ -224,6 +269,7 @@ def main():
             e1.record()
         e1.synchronize()
         dev_ms += e0.elapsed_time(e1)
+        leg1_ids = {k: eng.poll(ids[k], TOTAL_LEN)[0] for k in CHECK}   # after the timer
         eng.clear_finished()
     barrier()
     st = eng.stats()
@@ -234,11 +280,15 @@ def main():
     t0 = time.perf_counter()
     got = 0
     for _ in range(args.steps):
-        got += job(True)
+        n, leg2_ids = job(True)
+        got += n
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     clocks = sampler.stop()
     assert got == gen_per_job * args.steps
+    # same engine, same prompts: the device-timed leg and the end-to-end leg must have generated the same ids
+    for k in CHECK:
+        assert leg1_ids[k].tolist() == leg2_ids[k].tolist(), f"sequence {k}: ids differ between the two timed legs"
     st2 = eng.stats()
     ctx.check_device_status()
 
@@ -256,33 +306,44 @@ def main():
         attn_bytes = st["attn_bytes_total"] / max(1, st["attn_launches_timed"])
         achieved = attn_bytes / (attn_ms * 1e-3) / 1e9 if attn_ms > 0 else 0.0
         steps_per_job = st["steps"] / args.steps
+        # whole decode step against the HBM roofline: every weight once, the K/V of all 12 layers, the appends
+        n_dec = max(1, st["decode_steps_timed"])
+        step_ms = st["decode_step_gpu_ms_total"] / n_dec
+        step_bytes = st["decode_step_bytes_total"] / n_dec
+        step_achieved = step_bytes / (step_ms * 1e-3) / 1e9 if step_ms > 0 else 0.0
         line = {
             "metric": "decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "l2": "working set per engine step (247 MB weights + ~0.9 GB KV) exceeds the 126 MB L2",
-                       "engine_steps_per_job": steps_per_job, "generated_tokens_per_job": gen_per_job,
-                       "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps,
-                       "detached_prefill": args.detached_prefill},
+            "config": workload_config(ak),
             "e2e": {"value": e2e_value, "unit": "tok/s",
                     "h2d_bytes_per_step": (st2["h2d_bytes"] - st["h2d_bytes"]) / args.steps,
                     "d2h_bytes_per_step": (st2["d2h_bytes"] - st["d2h_bytes"]) / args.steps},
             "gpu_launches": int(st["kernel_launches"]),
-            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,2> (layer 0, every decode-only step)",
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,4> (layer 0, every decode-only step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind,
                          # DRAM bytes per launch: 1.059 x the algorithmic bytes, the ratio ncu measured
                          # (dram__bytes_read.sum + dram__bytes_write.sum) on a smaller launch of the same
                          # kernel; traffic grows in proportion to the K/V bytes
                          "traffic": 1.059 * attn_bytes,
-                         "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "launches_timed": st["attn_launches_timed"]},
+                         "bytes_per_launch": attn_bytes, "ms_per_launch": attn_ms, "launches_timed": st["attn_launches_timed"],
+                         # the whole decode-only engine step (a captured graph of ~100 launches) against the same peak
+                         "step": {"achieved": step_achieved, "frac": step_achieved / peak, "unit": "GB/s",
+                                  "bytes_per_step": step_bytes, "ms_per_step": step_ms, "steps_timed": st["decode_steps_timed"]}},
             "clocks": clocks,
             "engine": {"decode_tokens": st["decode_tokens"], "prefill_tokens": st["prefill_tokens"],
                        "graph_launches": st["graph_launches"], "eager_steps": st["eager_steps"],
-                       "host_counted_launches": int(eager_launches)},
+                       "host_counted_launches": int(eager_launches), "engine_steps_per_job": steps_per_job,
+                       "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps,
+                       "detached_prefill": args.detached_prefill,
+                       # rank 0, per job (one pass over the 256 sequences): where the time goes
+                       "gpu_ms_per_job": st["step_gpu_ms_total"] / args.steps,
+                       "launch_host_ms_per_job": st["launch_host_ms_total"] / args.steps,
+                       "ids_checked_between_legs": list(CHECK)},
         }
         if world == 1 and not args.no_cpu_baseline:
-            r = cpu_reference_arm(ak, 1, 0)
+            r = cpu_reference_arm(ak, 4, 0)
             line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line))
     eng.close(); w.close(); ctx.close()

@@ -168,7 +168,10 @@ AK_API int ak_sample_token(void* stream, const float* logits, uint32_t rows, uin
  *   slot(pos) = block_tables[row][pos/16]*16 + pos%16
  *   scratch: device buffer of ak_attn_decode_scratch_bytes() bytes, needed only when the
  *            launch splits sequences over several CTAs (n_splits > 1); may be NULL otherwise.
- *   n_splits: 0 = let the library choose. */
+ *            It holds the splits' partial results and one arrival counter per (row, head); the
+ *            call clears the counters itself, so the buffer may hold anything. The CTA that
+ *            arrives last merges the partials inside the same launch (no second kernel).
+ *   n_splits: 0 = let the library choose; at most 32. */
 typedef struct ak_attn_decode_params {
     uint32_t rows, heads, head_dim, block_size, max_blocks_per_seq;
     float scale;
@@ -187,14 +190,15 @@ AK_API int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool,
  * The split-KV partials go to a buffer built into the library image instead of caller scratch:
  *   - each GPU that loads the library holds that buffer (ak_attn_decode_noalloc_max_scratch_bytes(),
  *     8 MiB) until the process exits;
- *   - a launch whose partials (rows*heads*n_splits*(head_dim+2)*4 bytes) do not fit is refused with
- *     AK_ERR_UNSUPPORTED and a message; nothing is launched;
+ *   - a launch whose partials and counters (rows*heads*(n_splits*(head_dim+2)+1)*4 bytes) do not fit
+ *     is refused with AK_ERR_UNSUPPORTED and a message; nothing is launched;
  *   - the call makes no cudaMalloc/cudaFree and calls no allocating library routine;
  *   - the first call on a device looks up the buffer's device address (that device must be
  *     current); make that first call before starting any stream capture;
  *   - all calls on one GPU share the buffer: calls that may overlap on the GPU (different streams)
- *     race on it and must be ordered by the caller. Nothing needs clearing between calls: every
- *     partial that is read was written earlier in the same call. */
+ *     race on it and must be ordered by the caller. The buffer keeps the last call's contents:
+ *     every partial that is read was written earlier in the same call, and the arrival counters,
+ *     which must start at zero, are cleared on the stream by the call itself (a memset). */
 AK_API size_t ak_attn_decode_noalloc_max_scratch_bytes(void);
 AK_API int ak_attn_decode_paged_noalloc(void* stream, const void* q, const void* k_pool, const void* v_pool,
                                         const int32_t* block_tables, const int32_t* kv_lens, void* out,
@@ -372,6 +376,11 @@ typedef struct ak_engine_stats {
     uint64_t h2d_bytes, d2h_bytes; /* bytes the engine copied host->device / device->host */
     double step_gpu_ms_total;      /* device time of the captured steps (attn_timing) */
     double launch_host_ms_total;   /* host time spent launching the captured steps */
+    double decode_step_gpu_ms_total;  /* device time of the decode-only captured steps (attn_timing) */
+    uint64_t decode_steps_timed;
+    uint64_t decode_step_bytes_total; /* algorithmic bytes of those steps: every weight read once per step
+                                       * (embedding rows of the batch only), K/V of all layers read for
+                                       * every running sequence, one K/V position appended per sequence */
 } ak_engine_stats;
 AK_API int ak_engine_get_stats(ak_engine* e, ak_engine_stats* out);
 AK_API int ak_engine_reset_stats(ak_engine* e);

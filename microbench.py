@@ -1,7 +1,7 @@
 """Kernel microbenchmarks (one JSON line per kernel), timed with CUDA events on the launching stream.
 
-    python akasha-core_b200/microbench.py [attn] [gemm] [norm] [engine] [--iters N] [--small]
-                                          [--rows R] [--splits S] [--min-len L]   (attn only)
+    python microbench.py [attn] [gemm] [norm] [engine] [--iters N] [--small]
+                                          [--rows R] [--splits S] [--min-len L] [--max-len L]   (attn only)
 
   attn : ragged paged decode attention, 1024 sequences, 12 heads x 64, KV lengths U[1,512] (seed 3),
          bf16 K/V ~ N(0,1), block 16.  Reports algorithmic GB/s against the measured HBM peak.
@@ -9,6 +9,7 @@
   norm : fused RMSNorm + RoPE (+ residual) on 32768 x 768 rows, f32 in / bf16 out. Reports GB/s.
   engine : steady-state decode steps of the 162M engine with 64 ragged sequences in flight
          (not in the default set; the launch sequence to hand to a profiler).
+  session : batch-1 prefill + greedy decode through the session API, fp32 and bf16 (not in the default set).
 
 `--small` shrinks every case (for a profiler capture: inputs stay above the 126 MB L2 where it
 matters, a few launches, well under a GB on the device).
@@ -22,7 +23,7 @@ import sys
 
 import numpy as np
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
@@ -57,30 +58,40 @@ def timed(torch, fn, iters, warmup=3):
 def bench_attn(ak, torch, iters, small):
     rows, heads, hd, max_blocks = (256 if small else 1024), 12, 64, 32
     rows = int(_opt("--rows", rows))
-    splits = int(_opt("--splits", 1))
+    splits = int(_opt("--splits", 0))      # 0 = the library's own plan
     lo = int(_opt("--min-len", 1))
     hi = int(_opt("--max-len", 512))
     lens = ak.uniform_ints(rows, lo, hi, seed=3)
     n_blocks = rows * max_blocks
     g = torch.Generator(device="cuda").manual_seed(3)
-    kp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
-    vp = torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16()
+    # pools are rotated between launches so that together they exceed L2 (126 MB), as the 12 layers' pools do
+    # inside the engine: every launch streams its K/V from HBM
+    pool_bytes = 2 * n_blocks * heads * 16 * hd * 2
+    n_sets = max(1, min(8, -(-512 * 1024 * 1024 // pool_bytes)))
+    kps = [torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16() for _ in range(n_sets)]
+    vps = [torch.randn(n_blocks, heads, 16, hd, device="cuda", generator=g).bfloat16() for _ in range(n_sets)]
     perm = torch.randperm(n_blocks, device="cuda", generator=g).to(torch.int32).reshape(rows, max_blocks)
     q = torch.randn(rows, heads * hd, device="cuda", generator=g).bfloat16()
     out = torch.empty_like(q)
     kv_lens = torch.from_numpy(lens.astype(np.int32)).cuda()
     stream = torch.cuda.current_stream().cuda_stream
     nb = ak.ops.attn_decode_scratch_bytes(rows, heads, hd, max_blocks, splits, ak.AK_BF16)
-    scratch = torch.empty(max(nb, 16), dtype=torch.uint8, device="cuda")
-    fn = lambda: ak.ops.attn_decode_paged(q, kp, vp, perm, kv_lens, out, rows, heads, hd, max_blocks, 0.125,
-                                          ak.AK_BF16, splits, n_blocks, scratch, stream)
+    scratch = torch.zeros(max(nb, 16), dtype=torch.uint8, device="cuda")
+    it = [0]
+
+    def fn():
+        i = it[0] % n_sets
+        it[0] += 1
+        ak.ops.attn_decode_paged(q, kps[i], vps[i], perm, kv_lens, out, rows, heads, hd, max_blocks, 0.125,
+                                 ak.AK_BF16, splits, n_blocks, scratch, stream)
     ms = timed(torch, fn, iters)
     sumL = int(lens.sum())
     alg = sumL * heads * hd * 2 * 2 + rows * heads * hd * 2 * 2 + int(((lens + 15) // 16).sum()) * 4
     hbm, _, src = peaks()
     gbs = alg / (ms * 1e-3) / 1e9
-    return {"kernel": "attn_decode_paged_kernel<bf16,64>", "rows": rows, "n_splits": splits, "sum_kv_len": sumL, "ms": ms,
-            "algorithmic_bytes": alg, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm, "peak_source": src}
+    return {"kernel": "attn_decode_paged_kernel<bf16,64>", "rows": rows, "n_splits": splits or "auto", "pool_sets": n_sets,
+            "sum_kv_len": sumL, "ms": ms, "algorithmic_bytes": alg, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm,
+            "peak_source": src}
 
 
 def bench_gemm(ak, torch, iters, small):
@@ -105,10 +116,8 @@ def bench_gemm(ak, torch, iters, small):
 def bench_skinny(ak, torch, iters, small):
     """The four per-layer GEMMs of a 64-row decode step, each as a chain of 12 launches over 12
     different weight sets (170 MB in total, more than L2) replayed from a CUDA graph, so that
-    each launch sees the launch-to-launch overlap and the cold weights it sees inside the engine.
-    `--plans "16,1,6;32,1,6"` repeats every shape under those skinny-plan overrides."""
+    each launch sees the launch-to-launch overlap and the cold weights it sees inside the engine."""
     M = int(_opt("--m", 64))
-    plans = [p for p in str(_opt("--plans", "")).split(";") if p]
     shapes = [("qkv", 2304, 768, ak.EPI_STORE_F32), ("out", 768, 768, ak.EPI_ADD_F32),
               ("up", 3072, 768, ak.EPI_SILU_BF16), ("down", 768, 3072, ak.EPI_ADD_F32)]
     res = []
@@ -117,26 +126,19 @@ def bench_skinny(ak, torch, iters, small):
         wts = [(torch.randn(N, K, device="cuda") * 0.05).bfloat16() for _ in range(12)]
         pad = [torch.empty(9 * 1024 * 1024 // 2, device="cuda", dtype=torch.bfloat16) for _ in range(12)]  # spacing, as other layers' weights
         c = torch.zeros(M, N, device="cuda", dtype=torch.bfloat16 if epi == ak.EPI_SILU_BF16 else torch.float32)
-        for plan in ([None] + plans):
-            if plan is None:
-                os.environ.pop("AK_GEMM_PLAN", None)
-            else:
-                os.environ["AK_GEMM_PLAN"] = plan
-            side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                stream = side.cuda_stream
-                for wt in wts:
-                    ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, stream)
-                side.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, stream=side):
-                    for _ in range(4):
-                        for wt in wts:
-                            ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, torch.cuda.current_stream().cuda_stream)
-                ms = timed(torch, g.replay, iters)
-            res.append({"kernel": "gemm_bf16_kernel chain", "op": name, "m": M, "n": N, "k": K, "plan": plan or "default",
-                        "us_per_launch": 1e3 * ms / 48})
-        os.environ.pop("AK_GEMM_PLAN", None)
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            stream = side.cuda_stream
+            for wt in wts:
+                ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, stream)
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(4):
+                    for wt in wts:
+                        ak.ops.gemm_bf16(a, wt, c, M, N, K, epi, torch.cuda.current_stream().cuda_stream)
+            ms = timed(torch, g.replay, iters)
+        res.append({"kernel": "gemm_bf16_kernel chain", "op": name, "m": M, "n": N, "k": K, "us_per_launch": 1e3 * ms / 48})
         del a, wts, c, pad
     return res
 
@@ -214,18 +216,57 @@ def bench_engine(ak, torch, iters, small):
     return out
 
 
+def bench_session(ak, torch, iters, small):
+    """Batch-1 generation with the session API (the reference's own use: one sequence, one token per
+    step): 162M model, 512-token prompt, then 384 greedy decode steps (context 1024), in fp32 parity mode
+    and in bf16. Per decode step the weights are streamed once (494.2 MB fp32 / 247.1 MB bf16) plus the
+    sequence's K/V; the fraction is that stream against the measured HBM peak. Wall clock around the
+    library's own generate loop (prefill timed apart)."""
+    import time
+    cfg = ak.ModelConfig.akasha_hall_1()
+    hbm, _, src = peaks()
+    n_prompt, n_new = (128, 64) if small else (512, 384)
+    prompt = ak.uniform_tokens(n_prompt, cfg.vocab_size, seed=1)
+    out = []
+    for name, dt, esz in (("f32", ak.AK_F32, 4), ("bf16", ak.AK_BF16, 2)):
+        ctx = ak.Context(0)
+        w = ak.ModelWeights(ctx, cfg, dt)
+        w.init_synthetic(0, 0.02)
+        s = ak.InferenceSession(ctx, w, 1024)
+        best = None
+        for rep in range(2):   # the first pass captures the decode graph
+            s.replace_cache()
+            t0 = time.perf_counter()
+            tok = s.prefill(prompt, want_logits=False)
+            t1 = time.perf_counter()
+            for _ in range(n_new):
+                tok = s.decode_step(tok, want_logits=False)
+            t2 = time.perf_counter()
+            best = (t1 - t0, t2 - t1)
+        pf_s, dec_s = best
+        w_bytes = 123_551_232 * esz
+        kv_bytes = (n_prompt + n_new / 2) * 18_432 * esz
+        gbs = (w_bytes + kv_bytes) * n_new / dec_s / 1e9
+        out.append({"kernel": f"session batch-1 decode ({name})", "prompt": n_prompt, "decode_steps": n_new,
+                    "prefill_ms": pf_s * 1e3, "decode_tok/s": n_new / dec_s, "us_per_token": 1e6 * dec_s / n_new,
+                    "stream_bytes_per_token": w_bytes + kv_bytes, "GB/s": gbs, "peak_GB/s": hbm, "frac": gbs / hbm,
+                    "peak_source": src})
+        s.close(); w.close(); ctx.close()
+    return out
+
+
 def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     ak = entry.load_package()
-    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine", "skinny")]
+    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine", "skinny", "session")]
     iters = int(_opt("--iters", 20))
     small = "--small" in sys.argv
     which = args or ["attn", "gemm", "norm"]
     torch.cuda.set_device(0)
     for w in which:
-        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine, "skinny": bench_skinny}[w](ak, torch, iters, small)
+        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine, "skinny": bench_skinny, "session": bench_session}[w](ak, torch, iters, small)
         for line in (r if isinstance(r, list) else [r]):
             print(json.dumps(line))
     torch.cuda.synchronize()

@@ -2,7 +2,7 @@
 ctx 4096, ~1.4B parameters, bf16 random init): ragged sequences with prompts uniform in
 [128, 3072], each generating `--gen` tokens, continuous batching with `--max-seqs` in flight.
 
-    python akasha-core_b200/scaled_bench.py [--seqs 512] [--gen 128] [--max-seqs 64]
+    python scaled_bench.py [--seqs 512] [--gen 128] [--max-seqs 64]
     torchrun --nproc-per-node N ... scaled_bench.py             # sequences sharded over N GPUs
     torchrun --nproc-per-node 2 ... scaled_bench.py --tp 2      # 2-way tensor parallel (NCCL all-reduce)
 
@@ -17,7 +17,7 @@ import os
 import sys
 import time
 
-ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 

@@ -356,6 +356,46 @@ def test_engine_capacity_and_errors(ak, ctx):
     e.close(); w.close()
 
 
+def test_engine_rejects_sequence_larger_than_the_kv_pool(ak, ctx):
+    """A sequence reserves ceil(max_total_len/16) blocks at admission. With a caller-chosen pool smaller
+    than that it could never start: submit refuses it, and a queue that can never drain is an error
+    from ak_engine_run, not an endless host loop."""
+    cfg = ak.ModelConfig(100, 64, 1, 1, 64)
+    _, w = make(ak, ctx, cfg, 1, 0.1)
+    e = ak.Engine(ctx, w, max_seqs=2, max_seq_len=64, kv_blocks=2)   # 2 blocks = 32 positions in all
+    with pytest.raises(ak.AkashaError) as ei:
+        e.submit([1, 2, 3], 48)                                       # needs 3 blocks
+    assert ei.value.kind == "ContextFull" and "KV blocks" in str(ei.value)
+    a = e.submit([1, 2, 3], 32)                                       # 2 blocks: fits
+    b = e.submit([4, 5], 20)                                          # 2 blocks: waits for a's
+    assert e.run_to_completion() > 0
+    for i, n in ((a, 29), (b, 18)):
+        t, fin = e.poll(i)
+        assert fin and len(t) == n
+    e.close(); w.close()
+
+
+def test_session_parity_fp32_head_dim_4(ak, orc, ctx):
+    """f32 weights accept head_dim % 4 == 0: the fused RoPE + append and the generic attention
+    kernels must run such a model (the reference's smallest test shapes use head_dim 4)."""
+    cfg = ak.ModelConfig(61, 16, 4, 2, 24)    # dim 16, 4 heads: head_dim 4
+    params, w = make(ak, ctx, cfg, 3, 0.2)
+    prompt = ak.uniform_tokens(7, cfg.vocab_size, seed=9)
+    s = ak.InferenceSession(ctx, w, 24)
+    s.replace_cache()
+    logits, tok = s.prefill(prompt)
+    toks, all_logits = [tok], [logits]
+    for _ in range(9):
+        logits, tok = s.decode_step(toks[-1])
+        toks.append(tok)
+        all_logits.append(logits)
+    om = orc.Model(cfg.as_dict(), params)
+    st, want, ol = orc.Session(om, 24).generate_greedy(prompt, 10, want_logits=True)
+    assert list(want) == toks
+    assert max(float(np.max(np.abs(a - b))) for a, b in zip(all_logits, ol)) < 1e-3
+    s.close(); w.close()
+
+
 def test_session_bf16_fused_argmax_and_oracle_logits(ak, orc, ctx):
     """bf16 mode: the argmax fused into the lm_head epilogue equals the first maximum of the logits
     the same launch stored, and the logits track the oracle's bf16-emulating mode."""

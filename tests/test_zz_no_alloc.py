@@ -4,8 +4,9 @@ It exists for hosts that may not allocate device memory at call time: a plugin i
 framework's memory pool, a serving loop that forbids allocator calls once it is running, or a
 process that has already given all free HBM to its KV pool. Its split-KV partials live in a
 buffer inside the library image. This file checks, through the C ABI, that it returns what the
-ordinary entry point (caller-provided scratch) returns, on two calls in a row that reuse the
-shared buffer, and that an over-sized request is refused instead of overrunning the buffer.
+ordinary entry point (caller-provided scratch) returns and what the CPU oracle computes, on two
+calls in a row that reuse the shared buffer, and that an over-sized request is refused instead
+of overrunning the buffer.
 
 Collected last on purpose (file name): a failure here cannot hide any other test's result.
 """
@@ -29,8 +30,22 @@ def _case(torch, ak, rows, heads, hd, max_len, seed, dtype):
     return kp, vp, tables.contiguous(), q, torch.from_numpy(lens).cuda(), n_blocks, max_blocks
 
 
+def _oracle_rows(orc, kp, vp, tables, q, kv_lens, heads, hd, rows):
+    """The oracle's cached attention (src/shaders/cpu.rs:144-203) for a few rows, from the paged pools."""
+    kp, vp, q = kp.float().cpu().numpy(), vp.float().cpu().numpy(), q.float().cpu().numpy()
+    tables, kv_lens = tables.cpu().numpy(), kv_lens.cpu().numpy()
+    out = {}
+    for r in rows:
+        L = int(kv_lens[r])
+        pos = np.arange(L)
+        k = kp[tables[r, pos // 16], :, pos % 16, :].reshape(L, heads * hd)
+        v = vp[tables[r, pos // 16], :, pos % 16, :].reshape(L, heads * hd)
+        out[r] = orc.decode_attention(q[r].copy(), np.ascontiguousarray(k), np.ascontiguousarray(v), L, hd)
+    return out
+
+
 @pytest.mark.parametrize("dtype_name", ["bf16", "f32"])
-def test_noalloc_matches_scratch_entry_point_twice(ak, torch_cuda, dtype_name):
+def test_noalloc_matches_scratch_entry_point_twice(ak, orc, torch_cuda, dtype_name):
     torch = torch_cuda
     dtype = ak.AK_BF16 if dtype_name == "bf16" else ak.AK_F32
     tol = 1e-2 if dtype == ak.AK_BF16 else 2e-5      # the tolerances of test_attn_decode_paged
@@ -52,6 +67,10 @@ def test_noalloc_matches_scratch_entry_point_twice(ak, torch_cuda, dtype_name):
         w, g = want.float().cpu().numpy(), got.float().cpu().numpy()
         assert np.isfinite(g).all(), f"call {call}: non-finite output"
         assert np.max(np.abs(g - w)) <= tol, f"call {call}: differs from the scratch entry point"
+        # and against the CPU oracle directly (rows 0 = the longest sequence, 1 and the last one); values ~N(0,1),
+        # so the bf16 bound is the output's rounding step at |x| < 4
+        for r, want_row in _oracle_rows(orc, kp, vp, tables, q, kv_lens, heads, hd, (0, 1, rows - 1)).items():
+            assert np.max(np.abs(g[r] - want_row)) <= (3e-2 if dtype == ak.AK_BF16 else 1e-4), f"call {call}, row {r}: differs from the oracle"
 
 
 def test_noalloc_rejects_oversized_request(ak, torch_cuda):
