@@ -113,6 +113,7 @@ _PROTOS = {
     "ak_sample_token": [vp, vp, C.c_uint32, C.c_uint32, vp, vp, C.c_float, C.c_float, C.c_uint32, C.c_float, C.c_uint64, C.c_uint64, vp],
     "ak_attn_decode_paged": [vp, vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
     "ak_attn_decode_paged_noalloc": [vp, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
+    "ak_attn_decode_append_paged": [vp, vp, vp, C.c_uint32, vp, vp, vp, vp, vp, vp, AttnDecodeParams],
     "ak_attn_prefill_paged": [vp, vp, vp, vp, vp, C.c_uint32, vp, vp, vp] + [C.c_uint32] * 5 + [C.c_float, C.c_uint32, C.c_uint32],
     "ak_rope_kv_append": [vp, vp, vp, vp, vp, vp, vp] + [C.c_uint32] * 5,
     "ak_rmsnorm_rope_residual": [vp, vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32, C.c_uint32],

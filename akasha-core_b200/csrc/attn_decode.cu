@@ -21,6 +21,14 @@
 // CTA that arrives last merges the partials in split order (so the sum does not depend on who is
 // last) and clears the counter: one launch, no second kernel, no waiting on other CTAs.
 //
+// Fused form (the engine's decode rows): the kernel also does the reference's head split, RoPE and cache
+// append of the step's new token (head_gather x3 -> rope_offset x2 -> cache_write x2,
+// src/nn/inference_graphs.rs:385-426). Every warp rotates its own copy of the query straight from the qkv
+// projection's f32 output; the warp that owns the sequence's last KV block rotates the new key, stores the new
+// key and value rows to the pools and patches them into its shared-memory copy of that block. One launch less
+// per layer, and, as the preceding kernel (the qkv projection) never touches the cache, EVERY K/V tile is
+// requested before the programmatic-dependent-launch wait: the HBM stream overlaps the projection's tail.
+//
 // Every wait on an mbarrier is bounded; on expiry the kernel records a code in a status word
 // and unwinds.
 #include "kernels.h"
@@ -94,6 +102,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Fused split + RoPE + append (see the top of the file). qkv == nullptr: plain attention over q.
+struct DecFused {
+    const float* qkv;       // [rows, 3 * heads * HD] f32: q | k | v of the step's new token of every sequence
+    const float2* rope;     // [rope_len][HD / 2] (cos, sin)
+    uint32_t rope_len;
+    void* k_pool;           // the pools as plain pointers, for the append stores
+    void* v_pool;
+};
+
 // How a sequence of nblk KV blocks is divided: n_act CTAs (<= n_splits) of bps blocks each, every one
 // of them non-empty. A function of the sequence's own length only.
 __device__ __forceinline__ void split_plan(uint32_t nblk, uint32_t n_splits, uint32_t& n_act, uint32_t& bps) {
@@ -159,19 +176,31 @@ __device__ __forceinline__ void finish_row(float M, float L, float (&o)[HD / 32]
     if (lane == 0) *counter = 0u;
 }
 
+// Resident CTAs per SM the register budget must allow: with a 2-deep ring a CTA holds 33 KB (bf16, head_dim 64),
+// so shared memory admits 6, and 6 x 148 = 888 slots take a 64-sequence x 12-head batch in ONE wave.
+template <typename T, int HD, int ST> struct DecOcc {
+    static constexpr int SMEM = DecCfg<T, HD, ST>::SMEM_BYTES + 2048;
+    static constexpr int BY_SMEM = (227 * 1024) / SMEM;
+    static constexpr int VALUE = BY_SMEM > 6 ? 6 : (BY_SMEM < 1 ? 1 : BY_SMEM);
+};
+
 template <typename T, int HD, int ST>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+__global__ void __launch_bounds__(DEC_WARPS * 32, DecOcc<T, HD, ST>::VALUE)
 attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                          const T* __restrict__ q, const int32_t* __restrict__ block_tables,
                          const int32_t* __restrict__ kv_lens, T* __restrict__ out, float* __restrict__ scratch,
-                         uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits, uint32_t early) {
+                         uint32_t heads, uint32_t max_blocks, float scale, uint32_t n_splits, uint32_t early,
+                         const DecFused fz) {
     // `early` = the caller guarantees that the kernel launched just before this one wrote nothing of
-    // the cache except each sequence's newest position (the engine's append kernel), and nothing of the
-    // descriptor arrays. Then, under programmatic dependent launch, the lengths, the block tables and
-    // every KV block except the one holding the newest position are fetched BEFORE waiting for that
-    // kernel; q and the newest block come after. Without `early` nothing is read before the wait.
+    // the cache except each sequence's newest position (the engine's append kernel; in the fused form
+    // nothing of the cache at all), and nothing of the descriptor arrays. Then, under programmatic
+    // dependent launch, the lengths, the block tables and every KV block except one the predecessor may
+    // have written are fetched BEFORE waiting for that kernel; q (or qkv) comes after. Without `early`
+    // nothing is read before the wait.
     pdl_trigger();
     if (!early) pdl_wait();
+    const bool fused = fz.qkv != nullptr;
+    if (threadIdx.x == 0) { tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
     using C = DecCfg<T, HD, ST>;
     constexpr bool MMA = (sizeof(T) == 2);
     extern __shared__ uint8_t smem_raw[];
@@ -181,6 +210,11 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
 
     const uint32_t h = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int32_t* table = block_tables + (size_t)row * max_blocks;
+    // Unsplit launches know their blocks' table entries without the length: fetch both at once (one memory
+    // latency instead of two before the first tile can be requested). Entries past the sequence's end are never used.
+    uint32_t my_blk = 0;
+    if (n_splits == 1 && lane < (uint32_t)C::STAGES && warp + lane * DEC_WARPS < max_blocks) my_blk = (uint32_t)table[warp + lane * DEC_WARPS];
     const int32_t kv_len = kv_lens[row];
 
     // block range of this split
@@ -201,7 +235,6 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     }
     __syncwarp();
 
-    const int32_t* table = block_tables + (size_t)row * max_blocks;
     // blocks of this warp: b_begin + warp, + DEC_WARPS, ...
     const uint32_t first = b_begin + warp;
     const uint32_t nmine = (first < b_end) ? (b_end - first + DEC_WARPS - 1) / DEC_WARPS : 0;
@@ -223,11 +256,10 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     // holds the newest position (written by the preceding kernel) is held back until that kernel is
     // known to be complete
     const uint32_t pre = nmine < (uint32_t)C::STAGES ? nmine : (uint32_t)C::STAGES;
-    uint32_t my_blk = 0;
     bool deferred = false;
     if (lane < pre) {
-        my_blk = (uint32_t)table[first + lane * DEC_WARPS];
-        deferred = early && (first + lane * DEC_WARPS + 1 == nblk);
+        if (n_splits != 1) my_blk = (uint32_t)table[first + lane * DEC_WARPS];
+        deferred = early && !fused && (first + lane * DEC_WARPS + 1 == nblk);
         if (!deferred) issue(lane, my_blk);
     }
     if (early) pdl_wait();
@@ -237,6 +269,50 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     float m_run = -INFINITY, l_run = 0.0f;
     bool failed = false;
     const T* qrow = q + ((size_t)row * heads + h) * HD;
+    // fused form: this head's slices of the new token's q | k | v, and the RoPE factors of its position
+    const uint32_t dim = heads * HD;
+    const float* q32 = fused ? fz.qkv + (size_t)row * 3 * dim + (size_t)h * HD : nullptr;
+    const uint32_t new_pos = kv_len > 0 ? (uint32_t)kv_len - 1 : 0;
+    const float2* cs_row = fused ? fz.rope + (size_t)(new_pos < fz.rope_len ? new_pos : 0) * (HD / 2) : nullptr;
+    // q elements d, d+1 (d even) after RoPE, in the fused form
+    auto q_pair = [&](uint32_t d, float& a, float& b) {
+        const float2 x = *reinterpret_cast<const float2*>(q32 + d);
+        const float2 f = cs_row[d >> 1];
+        rope_rotate(x.x, x.y, f.x, f.y, a, b);
+    };
+    // The warp that owns the block holding the new position: rotate the new key, store the new key and value rows to
+    // the pools and patch them into the tile in shared memory (the tile was requested before they existed).
+    auto append_new = [&](uint32_t blk_phys, uint8_t* k_tile, uint8_t* v_tile) {
+        constexpr uint32_t CH = HD * (uint32_t)sizeof(T) / 16;   // 16-byte chunks per row
+        const uint32_t within = new_pos & (DEC_BS - 1);
+        for (uint32_t c = lane; c < 2 * CH; c += 32) {
+            const bool is_v = c >= CH;
+            const uint32_t cc = is_v ? c - CH : c, d0 = cc * C::EPC;
+            const float* src = q32 + (is_v ? 2 : 1) * dim + d0;
+            float x[C::EPC];
+#pragma unroll
+            for (int e = 0; e < C::EPC; e += 4) {
+                const float4 t4 = *reinterpret_cast<const float4*>(src + e);
+                x[e] = t4.x; x[e + 1] = t4.y; x[e + 2] = t4.z; x[e + 3] = t4.w;
+            }
+            if (!is_v) {
+#pragma unroll
+                for (int e = 0; e < C::EPC; e += 2) {
+                    const float2 f = cs_row[(d0 + e) >> 1];
+                    rope_rotate(x[e], x[e + 1], f.x, f.y, x[e], x[e + 1]);
+                }
+            }
+            alignas(16) T o[C::EPC];
+#pragma unroll
+            for (int e = 0; e < C::EPC; e++) o[e] = Cvt<T>::from_f(x[e]);
+            const uint4 pk = *reinterpret_cast<const uint4*>(o);
+            T* pool = reinterpret_cast<T*>(is_v ? fz.v_pool : fz.k_pool);
+            *reinterpret_cast<uint4*>(pool + (((size_t)blk_phys * heads + h) * DEC_BS + within) * HD + d0) = pk;
+            uint8_t* tile = is_v ? v_tile : k_tile;
+            *reinterpret_cast<uint4*>(tile + (cc >> 3) * (DEC_BS * 128) + within * 128 + (((cc & 7) ^ (within & 7)) << 4)) = pk;
+        }
+        __syncwarp();
+    };
 
     if constexpr (MMA) {
         // ---------------- bf16: tensor-core tiles -------------------------------------------------
@@ -246,10 +322,21 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         (void)g8;
         // A operand of Q.K^T: every row is q, so a0 == a1 and a2 == a3
         uint32_t qa[KS][2];
+        if (fused) {
 #pragma unroll
-        for (int ks = 0; ks < KS; ks++) {
-            qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
-            qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+            for (int ks = 0; ks < KS; ks++) {
+                float a, b;
+                q_pair(ks * 16 + 2 * t4, a, b);
+                qa[ks][0] = pack_bf16x2(a, b);
+                q_pair(ks * 16 + 8 + 2 * t4, a, b);
+                qa[ks][1] = pack_bf16x2(a, b);
+            }
+        } else {
+#pragma unroll
+            for (int ks = 0; ks < KS; ks++) {
+                qa[ks][0] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+                qa[ks][1] = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+            }
         }
         // per-lane ldmatrix row addresses inside a tile (swizzled): matrix mi = lane / 8, row r = lane % 8
         const uint32_t mi = lane >> 3, r8 = lane & 7;
@@ -271,6 +358,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const uint32_t blk_idx = first + i * DEC_WARPS;
             const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
             const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
+            if (fused && blk_idx + 1 == nblk)
+                append_new((uint32_t)table[blk_idx], my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
             if (n_valid < DEC_BS) {
                 // rows past the end of the sequence may hold anything (their probability is 0, but
                 // 0 * NaN would poison the tensor-core sum): clear them in the V tile
@@ -347,8 +436,19 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
         for (int g = 0; g < C::GROUPS; g++)
 #pragma unroll
             for (int c = 0; c < 4; c++) {
-                uint4 raw = *reinterpret_cast<const uint4*>(qrow + g * C::EPG + (4 * hh + c) * C::EPC);
-                unpack16<T>(raw, &qreg[(g * 4 + c) * C::EPC]);
+                if (fused) {
+                    // the rotated value is rounded to the cache dtype, as the unfused path stores and re-reads it
+#pragma unroll
+                    for (int e = 0; e < C::EPC; e += 2) {
+                        float a, b;
+                        q_pair(g * C::EPG + (4 * hh + c) * C::EPC + e, a, b);
+                        qreg[(g * 4 + c) * C::EPC + e] = Cvt<T>::to_f(Cvt<T>::from_f(a));
+                        qreg[(g * 4 + c) * C::EPC + e + 1] = Cvt<T>::to_f(Cvt<T>::from_f(b));
+                    }
+                } else {
+                    uint4 raw = *reinterpret_cast<const uint4*>(qrow + g * C::EPG + (4 * hh + c) * C::EPC);
+                    unpack16<T>(raw, &qreg[(g * 4 + c) * C::EPC]);
+                }
             }
         float acc[C::EPL];
 #pragma unroll
@@ -363,6 +463,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const uint32_t blk_idx = first + i * DEC_WARPS;
             const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
             const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
+            if (fused && blk_idx + 1 == nblk)
+                append_new((uint32_t)table[blk_idx], my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
 
             // ---- scores: position p, this lane's half of every 128-byte group
             float sc = 0.0f;
@@ -519,25 +621,36 @@ size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_di
     return partial_floats(rows, heads, head_dim, n_splits) * sizeof(float) + (size_t)rows * heads * sizeof(unsigned int);
 }
 
-// Launch plan. A large batch (>= 2 waves of one CTA per (sequence, head)) keeps the GPU busy by itself:
-// a 2-deep ring per warp (33 KB per CTA with bf16 head_dim 64, 6 CTAs = 24 warps per SM) and no splitting,
-// which would only add merges. A small batch is bound by its longest sequence: a 4-deep ring while a stage is
-// at most 4 KB, and enough splits that every warp owns at most one ring of blocks, so that a CTA requests all
-// of its K/V at once and a long sequence runs on several SMs.
+// Launch plan. The kernel's time is set by how many WAVES of CTAs the launch needs and by the longest chain of
+// ring rounds inside one CTA, not by bytes alone: a CTA's life is a chain of memory latencies (lengths and block
+// table, first tiles, one ring round per 2 blocks of a warp, merge). So: a 2-deep ring per warp (33 KB per CTA with
+// bf16 head_dim 64: 6 CTAs = 24 warps per SM, 888 slots, a 64-sequence x 12-head batch is ONE wave), and sequences
+// are split over several CTAs only while all CTAs still fit one wave (a single sequence or a handful of them: one CTA
+// per (sequence, head) would leave most SMs idle and run the whole length serially).
 #ifndef AK_DEC_SMALL_BATCH_STAGES
-#define AK_DEC_SMALL_BATCH_STAGES 4
+#define AK_DEC_SMALL_BATCH_STAGES 2
 #endif
-static bool small_batch(uint32_t rows, uint32_t heads) { return (uint64_t)rows * heads < 2 * 148 * 6; }
+static uint32_t stage_bytes_of(uint32_t head_dim, uint32_t kv_dtype) { return 2 * DEC_BS * head_dim * (kv_dtype == AK_F32 ? 4 : 2); }
+static uint32_t wave_slots(uint32_t head_dim, uint32_t kv_dtype, uint32_t stages) {
+    const uint32_t smem = DEC_WARPS * stages * stage_bytes_of(head_dim, kv_dtype) + 1024 + 2048;
+    uint32_t per_sm = (227 * 1024) / smem;
+    if (per_sm > 6) per_sm = 6;
+    if (per_sm < 1) per_sm = 1;
+    return 148 * per_sm;
+}
 static uint32_t ring_depth(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype) {
-    const uint32_t stage = 2 * DEC_BS * head_dim * (kv_dtype == AK_F32 ? 4 : 2);
-    return (stage <= 4096 && small_batch(rows, heads)) ? AK_DEC_SMALL_BATCH_STAGES : 2;
+    const bool small = (uint64_t)rows * heads <= wave_slots(head_dim, kv_dtype, AK_DEC_SMALL_BATCH_STAGES);
+    return (stage_bytes_of(head_dim, kv_dtype) <= 4096 && small) ? AK_DEC_SMALL_BATCH_STAGES : 2;
 }
 
 uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, uint32_t max_kv_len) {
-    if (rows == 0 || heads == 0 || !small_batch(rows, heads)) return 1;
+    const uint64_t items = (uint64_t)rows * heads;
+    if (items == 0) return 1;
+    const uint32_t st = ring_depth(rows, heads, head_dim, kv_dtype);
+    const uint32_t room = (uint32_t)(wave_slots(head_dim, kv_dtype, st) / items);   // CTAs per item that keep one wave
     const uint32_t max_blocks = (max_kv_len + DEC_BS - 1) / DEC_BS;
-    const uint32_t per_cta = DEC_WARPS * ring_depth(rows, heads, head_dim, kv_dtype);
-    uint32_t want = (max_blocks + per_cta - 1) / per_cta;
+    uint32_t want = (max_blocks + DEC_WARPS * st - 1) / (DEC_WARPS * st);           // every warp at most one ring of blocks
+    if (want > room) want = room;
     if (want > DEC_MAX_SPLITS) want = DEC_MAX_SPLITS;
     return want < 1 ? 1 : want;
 }
@@ -545,7 +658,7 @@ uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_di
 template <typename T, int HD, int ST>
 static int launch_fast_st(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                           const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
-                          const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
+                          const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows, const DecFused& fz) {
     using C = DecCfg<T, HD, ST>;
     CUtensorMap tmK, tmV;
     int rc = make_tmap_2d(&tmK, k_pool, sizeof(T), HD, pool_rows, (uint64_t)HD * sizeof(T), C::EPG, DEC_BS, TMA_SWIZZLE_128B);
@@ -565,18 +678,18 @@ static int launch_fast_st(cudaStream_t st, const void* q, const void* k_pool, co
     dim3 grid(p.heads, p.rows, n_splits);
     return launch_k(attn_decode_paged_kernel<T, HD, ST>, dim3(grid), dim3(DEC_WARPS * 32), C::SMEM_BYTES, st, NO_CLUSTER, tmK, tmV,
                     (const T*)q, block_tables, kv_lens, (T*)out, (float*)scratch, p.heads, p.max_blocks_per_seq, p.scale, n_splits,
-                    (uint32_t)(g_attn_early ? 1 : 0));
+                    (uint32_t)(g_attn_early ? 1 : 0), fz);
 }
 
 template <typename T, int HD>
 static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                        const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
-                       const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows) {
+                       const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows, const DecFused& fz) {
     if constexpr (2 * DEC_BS * HD * (int)sizeof(T) <= 4096 && AK_DEC_SMALL_BATCH_STAGES != 2) {
         if (ring_depth(p.rows, p.heads, HD, p.kv_dtype) != 2)
-            return launch_fast_st<T, HD, AK_DEC_SMALL_BATCH_STAGES>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
+            return launch_fast_st<T, HD, AK_DEC_SMALL_BATCH_STAGES>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows, fz);
     }
-    return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows);
+    return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows, fz);
 }
 
 // Rows of the 2-D view [n_blocks*heads*16, head_dim] of a pool. With pool_blocks given, a block
@@ -586,9 +699,31 @@ static uint64_t pool_rows_bound(const ak_attn_decode_params& p) {
     return (uint64_t)1 << 31;
 }
 
+static int launch_decode(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                         const ak_attn_decode_params& p, bool counters_are_zero, const DecFused& fz);
+
+bool attn_decode_fused_supported(uint32_t head_dim) { return head_dim == 64 || head_dim == 128; }
+
 int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                              const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
                              const ak_attn_decode_params& p, bool counters_are_zero) {
+    return launch_decode(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, counters_are_zero, DecFused{});
+}
+
+int launch_attn_decode_fused(cudaStream_t st, const float* qkv, const float2* rope_table, uint32_t rope_len, void* k_pool, void* v_pool,
+                             const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                             const ak_attn_decode_params& p, bool counters_are_zero) {
+    AK_REQUIRE(attn_decode_fused_supported(p.head_dim) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)qkv % 16 == 0),
+               AK_ERR_UNSUPPORTED, "attn_decode_fused: head_dim must be 64 or 128 and the buffers 16-byte aligned");
+    AK_REQUIRE(rope_table && rope_len, AK_ERR_INVALID_ARG, "attn_decode_fused: a RoPE table is required");
+    DecFused fz{qkv, rope_table, rope_len, k_pool, v_pool};
+    return launch_decode(st, qkv, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, counters_are_zero, fz);
+}
+
+static int launch_decode(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
+                         const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                         const ak_attn_decode_params& p, bool counters_are_zero, const DecFused& fz) {
     if (p.rows == 0 || p.heads == 0) return AK_OK;
     AK_REQUIRE(p.block_size == DEC_BS, AK_ERR_UNSUPPORTED, "attn_decode_paged: block_size must be 16");
     AK_REQUIRE(p.kv_dtype <= AK_BF16, AK_ERR_INVALID_ARG, "attn_decode_paged: bad kv_dtype");
@@ -620,11 +755,11 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
     }
     const uint64_t rows_bound = pool_rows_bound(p);
     if (p.kv_dtype == AK_F32) {
-        if (p.head_dim == 64) return launch_fast<float, 64>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound);
-        return launch_fast<float, 128>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound);
+        if (p.head_dim == 64) return launch_fast<float, 64>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound, fz);
+        return launch_fast<float, 128>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound, fz);
     }
-    if (p.head_dim == 64) return launch_fast<bf16, 64>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound);
-    return launch_fast<bf16, 128>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound);
+    if (p.head_dim == 64) return launch_fast<bf16, 64>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound, fz);
+    return launch_fast<bf16, 128>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, rows_bound, fz);
 }
 
 int attn_decode_status(unsigned int* out) {
@@ -645,6 +780,13 @@ int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool, const 
                          const int32_t* kv_lens, void* out, void* scratch, ak_attn_decode_params p) {
     AK_REQUIRE(q && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_paged: null pointer");
     return launch_attn_decode_paged(as_stream(stream), q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, false);
+}
+int ak_attn_decode_append_paged(void* stream, const float* qkv, const float* rope_table, uint32_t rope_len, void* k_pool, void* v_pool,
+                                const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch, ak_attn_decode_params p) {
+    AK_REQUIRE(qkv && rope_table && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_append_paged: null pointer");
+    AK_REQUIRE(p.block_size == DEC_BS && p.kv_dtype <= AK_BF16, AK_ERR_INVALID_ARG, "ak_attn_decode_append_paged: block_size must be 16, kv_dtype f32 or bf16");
+    return launch_attn_decode_fused(as_stream(stream), qkv, reinterpret_cast<const float2*>(rope_table), rope_len, k_pool, v_pool, block_tables,
+                                    kv_lens, out, scratch, p, false);
 }
 }
 

@@ -77,6 +77,14 @@ template <> struct Cvt<bf16> {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// RoPE rotation of one adjacent pair (src/shaders/cpu.rs:101-106): one rounding per operation (no fused
+// multiply-add), so that every kernel that rotates a pair -- the split + append kernel, the decode attention that
+// rotates its own query and new key -- produces the same bits, the bits of the reference's CPU arithmetic.
+__device__ __forceinline__ void rope_rotate(float x0, float x1, float cs, float sn, float& o0, float& o1) {
+    o0 = __fsub_rn(__fmul_rn(x0, cs), __fmul_rn(x1, sn));
+    o1 = __fadd_rn(__fmul_rn(x0, sn), __fmul_rn(x1, cs));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

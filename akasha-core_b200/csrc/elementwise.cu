@@ -66,6 +66,13 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
     pdl_wait();
     pdl_trigger();
     constexpr int RCACHE = 8;  // float4 per lane kept in registers -> size <= 1024 cached
+    // RoPE frequencies 1 / 10000^(2i / head_dim): head_dim / 2 values for the whole launch, computed once per CTA
+    __shared__ float s_freq[ROPE ? 128 : 1];
+    const bool freq_tab = ROPE && head_dim <= 256;
+    if (freq_tab) {
+        for (uint32_t i = threadIdx.x; i < head_dim / 2; i += blockDim.x) s_freq[i] = 1.0f / powf(10000.0f, (float)(2 * i) / (float)head_dim);
+        __syncthreads();
+    }
     uint32_t warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     uint32_t lane = threadIdx.x & 31;
     if (warp >= rows) return;
@@ -121,8 +128,8 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
     const bool same_d0 = ROPE && (128u % head_dim) == 0;
     float hs0 = 0.f, hc0 = 1.f, hs1 = 0.f, hc1 = 1.f;
     auto factors = [&](uint32_t d0, float& s0, float& c0, float& s1, float& c1) {
-        float f0 = 1.0f / powf(10000.0f, (float)d0 / (float)head_dim);
-        float f1 = 1.0f / powf(10000.0f, (float)(d0 + 2) / (float)head_dim);
+        float f0 = freq_tab ? s_freq[d0 >> 1] : 1.0f / powf(10000.0f, (float)d0 / (float)head_dim);
+        float f1 = freq_tab ? s_freq[(d0 >> 1) + 1] : 1.0f / powf(10000.0f, (float)(d0 + 2) / (float)head_dim);
         sincosf(pos * f0, &s0, &c0);
         sincosf(pos * f1, &s1, &c1);
     };
@@ -358,9 +365,8 @@ __global__ void rope_kv_append_kernel(const float* __restrict__ qkv, const int32
             sn = (float)sin((double)angle);
             cs = (float)cos((double)angle);
         }
-        float q0 = qv[i], q1 = qv[i + 1], k0 = kv[i], k1 = kv[i + 1];
-        qv[i] = q0 * cs - q1 * sn; qv[i + 1] = q0 * sn + q1 * cs;
-        kv[i] = k0 * cs - k1 * sn; kv[i + 1] = k0 * sn + k1 * cs;
+        rope_rotate(qv[i], qv[i + 1], cs, sn, qv[i], qv[i + 1]);
+        rope_rotate(kv[i], kv[i + 1], cs, sn, kv[i], kv[i + 1]);
     }
     alignas(16) T qo[VEC], ko[VEC], vo[VEC];
 #pragma unroll

@@ -412,7 +412,6 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
             float* hid = hidden_ + (size_t)r0 * D;
             void* xn = (char*)xn_ + (size_t)r0 * D * act;
             float* qkv = qkv_ + (size_t)r0 * 3 * Dq;
-            void* qb = (char*)qbuf_ + (size_t)r0 * Dq * act;
             void* at = (char*)attn_ + (size_t)r0 * Dq * act;
             void* up = (char*)up_ + (size_t)r0 * F * act;
             RC(launch_embed_rows(s, rw + 0, 4, d_sampled_, w_->embedding, dt, hid, V, D, nr));
@@ -420,7 +419,14 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                 const auto& b = w_->blocks[l];
                 RC(launch_rmsnorm(s, hid, b.norm_1, xn, dt, nullptr, nr, D, c.norm_eps));
                 RC(gemm_s(s, xn, b.qkv, qkv, nr, 3 * Dq, D, 0));
-                RC(launch_rope_kv_append(s, qkv, rw + 1, rw + 2, 4, qb, k_pool_[l], v_pool_[l], rope_table_, rope_len_, nr, H, hd, 16, dt));
+                // Decode rows get their head split, RoPE and cache append inside the attention kernel (head sizes the
+                // TMA kernel handles); the separate kernel then only serves the prompt rows of the range.
+                const bool fuse = dec && attn_decode_fused_supported(hd);
+                uint32_t a0 = r0, an = nr;
+                if (fuse) { a0 = max_seqs_; an = (r0 + nr > max_seqs_) ? r0 + nr - max_seqs_ : 0; }
+                if (an)
+                    RC(launch_rope_kv_append(s, qkv_ + (size_t)a0 * 3 * Dq, rows + (size_t)a0 * 4 + 1, rows + (size_t)a0 * 4 + 2, 4,
+                                             (char*)qbuf_ + (size_t)a0 * Dq * act, k_pool_[l], v_pool_[l], rope_table_, rope_len_, an, H, hd, 16, dt));
                 if (dec) {  // rows [0, max_seqs_): this range starts at row 0
                     ak_attn_decode_params p{};
                     p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
@@ -430,10 +436,17 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                         if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, s, cudaEventRecordExternal));
                         else AK_CUDA(cudaEventRecord(ev_attn0_, s));
                     }
-                    g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
-                    rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
+                    // the kernels launched since the descriptor upload wrote nothing of the cache but, at most, each decode
+                    // sequence's newest position (unfused) or a prompt's own blocks (the rows of another sequence)
+                    g_attn_early = true;
+                    if (fuse)
+                        rc = launch_attn_decode_fused(s, qkv_, rope_table_, rope_len_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables,
+                                                      d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
+                    else
+                        rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
                     g_attn_early = false;
                     if (rc) return rc;
+                    trace_mark("attn_decode");
                     if (timed) {
                         if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, s, cudaEventRecordExternal));
                         else AK_CUDA(cudaEventRecord(ev_attn1_, s));

@@ -115,6 +115,15 @@ def attn_decode_paged(q, k_pool, v_pool, block_tables, kv_lens, out, rows, heads
                                      _p(out), _p(scratch), p))
 
 
+def attn_decode_append_paged(qkv, rope_table, rope_len, k_pool, v_pool, block_tables, kv_lens, out, rows, heads, head_dim,
+                             max_blocks_per_seq, scale, kv_dtype=AK_BF16, n_splits=0, pool_blocks=0, scratch=None, stream=None):
+    """Decode attention with the new token's head split, RoPE and cache append fused in (`kv_lens`
+    counts the new token; `rope_table` is float32 [rope_len, head_dim/2, 2] = (cos, sin))."""
+    p = AttnDecodeParams(rows, heads, head_dim, 16, max_blocks_per_seq, scale, kv_dtype, n_splits, pool_blocks)
+    check(lib().ak_attn_decode_append_paged(_s(stream), _p(qkv), _p(rope_table), rope_len, _p(k_pool), _p(v_pool),
+                                            _p(block_tables), _p(kv_lens), _p(out), _p(scratch), p))
+
+
 def attn_decode_paged_noalloc(q, k_pool, v_pool, block_tables, kv_lens, out, rows, heads, head_dim, max_blocks_per_seq,
                               scale, kv_dtype=AK_BF16, n_splits=0, pool_blocks=0, stream=None):
     """`attn_decode_paged` for callers that must not allocate: the split-KV partials live in a

@@ -184,6 +184,18 @@ AK_API int ak_attn_decode_paged(void* stream, const void* q, const void* k_pool,
                                 const int32_t* block_tables, const int32_t* kv_lens, void* out,
                                 void* scratch, ak_attn_decode_params p);
 
+/* Decode attention with the step's head split, RoPE and cache append fused in (head_dim 64 or 128): for every row,
+ * the new token's q | k | v come from qkv [rows, 3*heads*head_dim] f32 (the qkv projection's output), its position
+ * is kv_lens[row] - 1 (kv_lens counts the new token) and its slot block_tables[row][pos/16]*16 + pos%16. The kernel
+ * rotates q and k (head_gather x3 -> rope_offset x2, src/nn/inference_graphs.rs:385-412; adjacent pairs,
+ * src/shaders/cuda.rs:224-254), stores K (post-RoPE) and V (raw) at that slot (cache_write x2,
+ * inference_graphs.rs:413-426) and attends over positions 0..pos (inference_graphs.rs:428-456).
+ * rope_table: float2 (cos, sin) [rope_len][head_dim/2] of angle = (float)pos / powf(10000, 2i/head_dim);
+ * every position must be < rope_len. Rows with kv_lens == 0 are skipped (zero output, nothing appended). */
+AK_API int ak_attn_decode_append_paged(void* stream, const float* qkv, const float* rope_table, uint32_t rope_len,
+                                       void* k_pool, void* v_pool, const int32_t* block_tables, const int32_t* kv_lens,
+                                       void* out, void* scratch, ak_attn_decode_params p);
+
 /* The same attention for callers that cannot allocate device memory when they call it (a plugin
  * living inside another framework's memory pool, a loop that bans allocator calls after start-up,
  * a process whose free HBM has all gone to the KV pool). It has no counterpart in the reference.

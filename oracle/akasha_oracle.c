@@ -5,11 +5,17 @@
  * against. Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may load
  * it. Nothing in the shipped library links or calls it.
  *
- * Parity status: the reference (Rust, with its GEMM/GEMV arithmetic in the absent `wilupgu`
- * crate) cannot be compiled or run here and stores no golden vectors, so BIT-LEVEL PARITY IS
- * UNPINNED. Semantic parity is pinned by restating the reference's own in-test plain math
- * (src/nn/ops/emit.rs:931-999, 1385-1411, 1449-1455; src/nn/sampling.rs:97-141) and holding
- * this file to the tolerances those tests use.
+ * Parity status: PINNED TO OUTPUTS OF THE REFERENCE'S OWN KERNEL CODE for every kernel whose source
+ * the reference holds: make_ref.py (beside this file) compiles the CUDA C kernel strings of
+ * src/shaders/cuda.rs unchanged (embedding, silu, rope, rope_offset, head_gather, attn_qk_cached,
+ * softmax_rect, attn_av_cached, rmsnorm, cache_write, flash_attention) and writes their outputs
+ * to tests/golden/reference_kernels.npz; tests/test_oracle_reference_kernels.py holds this file
+ * to them, bit-exact except where the summation order differs (rmsnorm).
+ * Still unpinned at the bit level: GEMM/GEMV (their arithmetic lives in the `wilupgu` crate,
+ * absent from the reference tree; the order here is the one the reference's own test pins
+ * within 1e-4, src/nn/ops/emit.rs:1449-1455) and the Rust host code (sampling), which are held
+ * to the reference's in-test math and known answers (src/nn/ops/emit.rs:931-999, 1385-1411;
+ * src/nn/sampling.rs:97-141).
  *
  * Each function cites the reference file:line whose arithmetic it follows. All arithmetic is
  * f32 with mul and add kept separate (compile with -ffp-contract=off): Rust never contracts

@@ -87,6 +87,62 @@ def test_attn_decode_paged(ak, orc, torch_cuda, dtype, heads, hd, lens, n_splits
     assert np.max(np.abs(got - want)) < tol
 
 
+@pytest.mark.parametrize("dtype", [0, 1])
+@pytest.mark.parametrize("heads,hd,lens,n_splits", [
+    (12, 64, [1, 2, 15, 16, 17, 32, 33, 64, 65, 200, 511, 512, 0, 49], 1),
+    (12, 64, [1, 16, 17, 65, 200, 512, 300], 3),         # the split that owns the last block appends
+    (4, 128, [1, 17, 128, 129, 700], 1),
+    (2, 64, [900, 33], 0),
+])
+def test_attn_decode_append_paged(ak, orc, torch_cuda, dtype, heads, hd, lens, n_splits):
+    """Fused head split + RoPE + cache append + attention equals head_gather -> rope_offset -> cache_write ->
+    attn_qk_cached -> softmax_rect -> attn_av_cached of the reference's decode graph
+    (src/nn/inference_graphs.rs:385-456): the output, and the K/V rows written at the new slots."""
+    torch = torch_cuda
+    rows, dim = len(lens), heads * hd
+    kp, vp, tables, ks, vs, n_blocks, max_blocks = build_paged(torch, orc, lens, heads, hd, dtype)
+    tdt = torch.float32 if dtype == 0 else torch.bfloat16
+    rnd = (lambda a: orc.round_bf16(np.ascontiguousarray(a, np.float32))) if dtype == 1 else (lambda a: np.asarray(a, np.float32))
+    qkv = orc.lcg(rows * 3 * dim, 77).reshape(rows, 3 * dim)
+    rope_len = max(lens) + 3
+    pos = np.arange(rope_len, dtype=np.float32)[:, None]
+    freq = (np.float32(1.0) / np.power(np.float32(10000.0), np.arange(0, hd, 2, dtype=np.float32) / np.float32(hd))).astype(np.float32)
+    ang = (pos * freq[None, :]).astype(np.float32)
+    table = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+    q_rot = np.zeros((rows, dim), np.float32)
+    for r, L in enumerate(lens):
+        if L == 0:
+            continue
+        p = L - 1
+        q_rot[r] = rnd(orc.rope(qkv[r:r + 1, :dim].copy(), hd, p)[0])
+        ks[r][p] = rnd(orc.rope(qkv[r:r + 1, dim:2 * dim].copy(), hd, p)[0])     # the appended rows
+        vs[r][p] = rnd(qkv[r, 2 * dim:])
+        blk, w = int(tables[r, p // 16]), p % 16
+        kp[blk, :, w, :] = float("nan")                                          # the kernel must write them
+        vp[blk, :, w, :] = float("nan")
+    out = torch.full((rows, dim), float("nan"), device="cuda", dtype=tdt)
+    kv_lens = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    nbytes = ak.ops.attn_decode_scratch_bytes(rows, heads, hd, max_blocks, n_splits, dtype)
+    scratch = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    ak.ops.attn_decode_append_paged(torch.from_numpy(qkv).cuda(), torch.from_numpy(table).cuda(), rope_len, kp, vp, tables, kv_lens, out,
+                                    rows, heads, hd, max_blocks, scale, dtype, n_splits, n_blocks, scratch)
+    torch.cuda.synchronize()
+    want = ref_decode(orc, q_rot, ks, vs, hd)
+    got, gk, gv = host(out), host(kp), host(vp)
+    assert np.isfinite(got).all()
+    tol = 2e-5 if dtype == 0 else 1e-2
+    assert np.max(np.abs(got - want)) < tol
+    for r, L in enumerate(lens):
+        if L == 0:
+            continue
+        p = L - 1
+        blk, w = int(tables[r, p // 16]), p % 16
+        slot_tol = 2e-6 if dtype == 0 else 8e-3        # one bf16 rounding step at |x| < 2
+        assert np.max(np.abs(gk[blk, :, w, :].reshape(-1) - ks[r][p])) < slot_tol
+        assert np.max(np.abs(gv[blk, :, w, :].reshape(-1) - vs[r][p])) < slot_tol
+
+
 def test_attn_decode_scaling_property(ak, orc, torch_cuda):
     """Size-independent property at the microbench shape family: attention output is a convex
     combination of V rows, so with V == const the output is that const, whatever K and the lengths."""
