@@ -151,6 +151,8 @@ _PROTOS = {
     "ak_engine_poll": [vp, C.c_uint64, u32p, C.c_uint32, u32p, C.POINTER(C.c_int)],
     "ak_engine_block_table": [vp, C.c_uint64, i32p, C.c_uint32, u32p],
     "ak_engine_clear_finished": [vp],
+    "ak_session_generate": [vp, u32p, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32, C.c_float, C.c_float, C.c_uint64, C.c_int, u32p,
+                            u32p],
     "ak_engine_get_stats": [vp, C.POINTER(EngineStats)],
     "ak_engine_reset_stats": [vp],
 }
@@ -454,13 +456,20 @@ class InferenceSession:
                                            C.byref(am)))
         return (logits, am.value) if want_logits else am.value
 
-    def generate(self, prompt_tokens, max_new_tokens: int, stop_on_eos: bool = True):
-        """Greedy `generate` (temperature <= 0, repetition_penalty == 1); returns token ids."""
+    def generate(self, prompt_tokens, max_new_tokens: int, stop_on_eos: bool = True, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, repetition_penalty: float = 1.0, seed: int = 0):
+        """`generate` (src/nn/inference.rs:264-326); returns token ids. With the defaults it is the greedy
+        path (temperature <= 0, repetition_penalty == 1); any other setting samples on the device with
+        `sample_token`'s rules (`run_chat` uses 0.8, 40, 0.95, 1.15)."""
         t = np.ascontiguousarray(prompt_tokens, np.uint32)
         out = np.zeros(max(1, max_new_tokens), np.uint32)
         n = C.c_uint32(0)
-        check(lib().ak_session_generate_greedy(self.h, t.ctypes.data_as(u32p), t.size, max_new_tokens,
-                                               int(stop_on_eos), out.ctypes.data_as(u32p), C.byref(n)))
+        if temperature <= 0.0 and repetition_penalty == 1.0:
+            check(lib().ak_session_generate_greedy(self.h, t.ctypes.data_as(u32p), t.size, max_new_tokens,
+                                                   int(stop_on_eos), out.ctypes.data_as(u32p), C.byref(n)))
+        else:
+            check(lib().ak_session_generate(self.h, t.ctypes.data_as(u32p), t.size, max_new_tokens, temperature, top_k, top_p,
+                                            repetition_penalty, seed, int(stop_on_eos), out.ctypes.data_as(u32p), C.byref(n)))
         return out[:n.value].copy()
 
     def read_cache(self, layer: int):

@@ -627,9 +627,7 @@ size_t attn_decode_scratch_bytes(uint32_t rows, uint32_t heads, uint32_t head_di
 // bf16 head_dim 64: 6 CTAs = 24 warps per SM, 888 slots, a 64-sequence x 12-head batch is ONE wave), and sequences
 // are split over several CTAs only while all CTAs still fit one wave (a single sequence or a handful of them: one CTA
 // per (sequence, head) would leave most SMs idle and run the whole length serially).
-#ifndef AK_DEC_SMALL_BATCH_STAGES
-#define AK_DEC_SMALL_BATCH_STAGES 2
-#endif
+constexpr uint32_t DEC_STAGES = 2;   // measured: a 4-deep ring (3 CTAs per SM) needs two waves for the same batch and is slower
 static uint32_t stage_bytes_of(uint32_t head_dim, uint32_t kv_dtype) { return 2 * DEC_BS * head_dim * (kv_dtype == AK_F32 ? 4 : 2); }
 static uint32_t wave_slots(uint32_t head_dim, uint32_t kv_dtype, uint32_t stages) {
     const uint32_t smem = DEC_WARPS * stages * stage_bytes_of(head_dim, kv_dtype) + 1024 + 2048;
@@ -638,15 +636,10 @@ static uint32_t wave_slots(uint32_t head_dim, uint32_t kv_dtype, uint32_t stages
     if (per_sm < 1) per_sm = 1;
     return 148 * per_sm;
 }
-static uint32_t ring_depth(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype) {
-    const bool small = (uint64_t)rows * heads <= wave_slots(head_dim, kv_dtype, AK_DEC_SMALL_BATCH_STAGES);
-    return (stage_bytes_of(head_dim, kv_dtype) <= 4096 && small) ? AK_DEC_SMALL_BATCH_STAGES : 2;
-}
-
 uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, uint32_t max_kv_len) {
     const uint64_t items = (uint64_t)rows * heads;
     if (items == 0) return 1;
-    const uint32_t st = ring_depth(rows, heads, head_dim, kv_dtype);
+    const uint32_t st = DEC_STAGES;
     const uint32_t room = (uint32_t)(wave_slots(head_dim, kv_dtype, st) / items);   // CTAs per item that keep one wave
     const uint32_t max_blocks = (max_kv_len + DEC_BS - 1) / DEC_BS;
     uint32_t want = (max_blocks + DEC_WARPS * st - 1) / (DEC_WARPS * st);           // every warp at most one ring of blocks
@@ -685,11 +678,7 @@ template <typename T, int HD>
 static int launch_fast(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                        const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
                        const ak_attn_decode_params& p, uint32_t n_splits, uint64_t pool_rows, const DecFused& fz) {
-    if constexpr (2 * DEC_BS * HD * (int)sizeof(T) <= 4096 && AK_DEC_SMALL_BATCH_STAGES != 2) {
-        if (ring_depth(p.rows, p.heads, HD, p.kv_dtype) != 2)
-            return launch_fast_st<T, HD, AK_DEC_SMALL_BATCH_STAGES>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows, fz);
-    }
-    return launch_fast_st<T, HD, 2>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows, fz);
+    return launch_fast_st<T, HD, (int)DEC_STAGES>(st, q, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, n_splits, pool_rows, fz);
 }
 
 // Rows of the 2-D view [n_blocks*heads*16, head_dim] of a pool. With pool_blocks given, a block

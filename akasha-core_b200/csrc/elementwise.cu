@@ -793,6 +793,122 @@ __device__ __forceinline__ uint64_t smp_mix(uint64_t z) {
     return z ^ (z >> 31);
 }
 
+// ---- no top-k truncation (top_k == 0, src/nn/sampling.rs:41-43): the candidate list is the whole vocabulary.
+// Instead of sorting 50k (logit, id) pairs, the two places where the reference walks its sorted list -- the top-p
+// cut and the draw -- are found by bisection on the logit value: "the mass of every candidate whose logit is
+// >= x" is a block-wide sum, and 32 such sums locate, bit by bit, the value at which the walk would stop; ties at
+// that value are then taken in index order, as the sorted list orders them.
+// Order-preserving map float -> uint32 (larger float, larger key); NaN sorts below everything.
+__device__ __forceinline__ uint32_t smp_key(float v) {
+    if (v != v) return 0u;
+    const uint32_t b = __float_as_uint(v);
+    const uint32_t k = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return k == 0u ? 1u : k;
+}
+// Sum over the row of exp((v - mx) / T) for candidates with key >= theta (all threads get the result), and their count.
+__device__ double smp_mass_ge(const float* srow, uint32_t n, uint32_t theta, double mx, double T, double* red, uint32_t* cnt_out) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    double acc = 0.0;
+    uint32_t cnt = 0;
+    for (uint32_t i = tid; i < n; i += SMP_THREADS) {
+        const float v = srow[i];
+        if (smp_key(v) >= theta && v == v) { acc += exp(((double)v - mx) / T); cnt++; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { acc += __shfl_xor_sync(0xffffffffu, acc, o); cnt += __shfl_xor_sync(0xffffffffu, cnt, o); }
+    __syncthreads();   // red is reused between calls
+    if (lane == 0) { red[warp] = acc; red[32 + warp] = (double)cnt; }
+    __syncthreads();
+    double tot = 0.0, c = 0.0;
+    for (int w = 0; w < SMP_THREADS / 32; w++) { tot += red[w]; c += red[32 + w]; }   // same order in every thread
+    if (cnt_out) *cnt_out = (uint32_t)c;
+    return tot;
+}
+// Largest key theta with mass(theta) >= target (strict == false) or > target (strict == true); mass(0) covers the row.
+__device__ uint32_t smp_bisect(const float* srow, uint32_t n, double target, bool strict, double mx, double T, double* red) {
+    uint32_t theta = 0;
+    for (int b = 31; b >= 0; b--) {
+        const uint32_t t2 = theta | (1u << b);
+        const double m = smp_mass_ge(srow, n, t2, mx, T, red, nullptr);
+        if (strict ? (m > target) : (m >= target)) theta = t2;
+    }
+    return theta;
+}
+// The whole-vocabulary sampler; called by every thread of the CTA, returns the pick in every thread.
+__device__ uint32_t smp_sample_untruncated(const float* srow, uint32_t n, float temperature, float top_p, double r, double* red,
+                                           uint32_t* scan) {
+    const uint32_t tid = threadIdx.x;
+    const double T = (double)temperature;
+    // max of the row = the first candidate
+    float best = -INFINITY;
+    for (uint32_t i = tid; i < n; i += SMP_THREADS) best = fmaxf(best, srow[i]);
+    best = warp_max(best);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = (double)best;
+    __syncthreads();
+    double mx = red[0];
+    for (int w = 1; w < SMP_THREADS / 32; w++) mx = fmax(mx, red[w]);
+    uint32_t n_all = 0;
+    const double total = smp_mass_ge(srow, n, 1u, mx, T, red, &n_all);
+    if (n_all == 0) return 0u;
+    // ---- top-p: the shortest prefix of the sorted list whose probability reaches top_p
+    uint32_t cut = 1u, cut_keep = 0xffffffffu;     // keys > cut are all kept, of the ties at `cut` the first cut_keep
+    double kept = total;
+    if (top_p < 1.0f) {
+        const double target = (double)top_p * total;
+        cut = smp_bisect(srow, n, target, false, mx, T, red);
+        uint32_t c_ge = 0, c_gt = 0;
+        const double m_ge = smp_mass_ge(srow, n, cut, mx, T, red, &c_ge);
+        const double m_gt = cut == 0xffffffffu ? 0.0 : smp_mass_ge(srow, n, cut + 1u, mx, T, red, &c_gt);
+        const uint32_t ties = c_ge - c_gt;
+        const double e_tie = ties ? (m_ge - m_gt) / (double)ties : 0.0;
+        uint32_t t = ties;
+        if (e_tie > 0.0) {
+            const double need = ceil((target - m_gt) / e_tie);
+            t = need < 1.0 ? 1u : (need > (double)ties ? ties : (uint32_t)need);
+        }
+        cut_keep = t;
+        kept = m_gt + (double)t * e_tie;
+    }
+    // ---- the draw: walk the kept prefix until the cumulative probability passes r
+    const double R = r * kept;
+    uint32_t phi = smp_bisect(srow, n, R, true, mx, T, red);
+    if (phi < cut) phi = cut;                        // rounding pushed the walk past the prefix: its last element
+    uint32_t c_ge = 0, c_gt = 0;
+    const double m_ge = smp_mass_ge(srow, n, phi, mx, T, red, &c_ge);
+    const double m_gt = phi == 0xffffffffu ? 0.0 : smp_mass_ge(srow, n, phi + 1u, mx, T, red, &c_gt);
+    uint32_t ties = c_ge - c_gt;
+    if (phi == cut && cut_keep < ties) ties = cut_keep;
+    const double e_tie = (c_ge - c_gt) ? (m_ge - m_gt) / (double)(c_ge - c_gt) : 0.0;
+    uint32_t t_idx = 0;
+    if (e_tie > 0.0 && R > m_gt) {
+        const double q = floor((R - m_gt) / e_tie);
+        t_idx = q >= (double)ties ? ties - 1 : (uint32_t)q;
+    }
+    if (ties == 0) return 0u;
+    // ---- the t_idx-th candidate (ascending id) whose key is phi: every thread counts a contiguous range of ids
+    const uint32_t chunk = (n + SMP_THREADS - 1) / SMP_THREADS;
+    const uint32_t lo = tid * chunk, hi = lo + chunk < n ? lo + chunk : n;
+    uint32_t mine = 0;
+    for (uint32_t i = lo; i < hi; i++) mine += (smp_key(srow[i]) == phi && srow[i] == srow[i]) ? 1u : 0u;
+    __syncthreads();
+    scan[tid] = mine;
+    __syncthreads();
+    uint32_t before = 0;
+    for (uint32_t w = 0; w < tid; w++) before += scan[w];
+    __syncthreads();
+    if (t_idx >= before && t_idx < before + mine) {
+        uint32_t k = t_idx - before;
+        for (uint32_t i = lo; i < hi; i++)
+            if (smp_key(srow[i]) == phi && srow[i] == srow[i]) {
+                if (k == 0) { scan[SMP_THREADS] = i; break; }
+                k--;
+            }
+    }
+    __syncthreads();
+    return scan[SMP_THREADS];
+}
+
 __global__ void __launch_bounds__(SMP_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, uint32_t n, uint32_t ld, const uint32_t* __restrict__ seen,
                    const uint32_t* __restrict__ seen_off, float penalty, float temperature, uint32_t top_k, float top_p,
@@ -801,8 +917,8 @@ sample_rows_kernel(const float* __restrict__ logits, uint32_t n, uint32_t ld, co
     uint32_t* bits = reinterpret_cast<uint32_t*>(srow + n);
     __shared__ float wv[32];
     __shared__ uint32_t wi[32];
-    __shared__ float cand_v[SMP_MAX_K];
-    __shared__ uint32_t cand_i[SMP_MAX_K];
+    __shared__ __align__(8) float cand_v[SMP_MAX_K];
+    __shared__ uint32_t cand_i[SMP_MAX_K + 1];
     const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (row_active && row_active[row] < 0) return;
     const float* l = logits + (size_t)row * ld;
@@ -819,6 +935,15 @@ sample_rows_kernel(const float* __restrict__ logits, uint32_t n, uint32_t ld, co
         for (uint32_t i = tid; i < n; i += SMP_THREADS)
             if (bits[i >> 5] & (1u << (i & 31))) srow[i] = srow[i] > 0.0f ? srow[i] / penalty : srow[i] * penalty;
         __syncthreads();
+    }
+    if (temperature > 0.0f && (top_k == 0 || top_k >= n)) {
+        // no truncation: bisection over the whole row (the selection loop below only serves small k)
+        double* red = reinterpret_cast<double*>(cand_v);          // 64 doubles
+        const uint64_t bitsr = smp_mix(seed ^ smp_mix(step * 0x632BE59BD9B4E019ull + row + 1));
+        const double r = (double)(bitsr >> 11) * (1.0 / 9007199254740992.0);
+        const uint32_t pick = smp_sample_untruncated(srow, n, temperature, top_p, r, red, cand_i);
+        if (tid == 0) out_idx[row] = pick;
+        return;
     }
     const uint32_t k = (temperature <= 0.0f) ? 1u : top_k;
     for (uint32_t c = 0; c < k; c++) {
@@ -889,8 +1014,8 @@ int launch_sample_rows(cudaStream_t st, const float* logits, uint32_t rows, uint
                        const uint32_t* seen_off, float penalty, float temperature, uint32_t top_k, float top_p, uint64_t seed,
                        uint64_t step, const int32_t* row_active, uint32_t* out_idx) {
     if (rows == 0 || n == 0) return AK_OK;
-    AK_REQUIRE(temperature <= 0.0f || (top_k >= 1 && top_k <= SMP_MAX_K), AK_ERR_UNSUPPORTED,
-               "sampler: top_k must be in 1..%d on the device (got %u); top_k = 0 (no truncation) needs a full sort", SMP_MAX_K, top_k);
+    AK_REQUIRE(temperature <= 0.0f || top_k <= SMP_MAX_K || top_k >= n, AK_ERR_UNSUPPORTED,
+               "sampler: top_k must be 0 (no truncation) or 1..%d on the device (got %u)", SMP_MAX_K, top_k);
     const size_t smem = (size_t)n * 4 + (size_t)((n + 31) / 32) * 4;
     AK_REQUIRE(smem <= 214 * 1024, AK_ERR_UNSUPPORTED, "sampler: vocabulary of %u does not fit shared memory", n);
     AK_CUDA(cudaFuncSetAttribute(sample_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

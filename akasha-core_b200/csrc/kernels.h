@@ -29,6 +29,10 @@ int launch_rope_kv_append(cudaStream_t st, const float* qkv, const int32_t* posi
 int launch_argmax(cudaStream_t st, const float* logits, uint32_t rows, uint32_t n, uint32_t ld,
                   const int32_t* row_active, uint32_t* out_idx);
 int launch_silu(cudaStream_t st, float* x, uint64_t n);
+// sample_token (src/nn/sampling.rs:18-81) per row; seen ids of row r are seen[seen_off[r] .. seen_off[r+1]).
+int launch_sample_rows(cudaStream_t st, const float* logits, uint32_t rows, uint32_t n, uint32_t ld, const uint32_t* seen,
+                       const uint32_t* seen_off, float penalty, float temperature, uint32_t top_k, float top_p, uint64_t seed,
+                       uint64_t step, const int32_t* row_active, uint32_t* out_idx);
 int launch_f32_to_bf16(cudaStream_t st, const float* src, void* dst, uint64_t n);
 int launch_bf16_to_f32(cudaStream_t st, const void* src, float* dst, uint64_t n);
 int launch_transpose_to_bf16(cudaStream_t st, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);

@@ -106,6 +106,9 @@ class Runner {
     int read_logits(uint32_t slot, float* host_out);
     int gather_cache(uint32_t layer, const int32_t* h_table, uint32_t len, float* k_out, float* v_out);
 
+    const float* logits_dev() const { return logits_; }     // [max_seqs][logits_ld()] f32, written when keep_logits
+    uint32_t logits_ld() const { return logits_ld_; }
+    uint32_t* sampled_dev() { return d_sampled_; }           // the token every slot feeds to its next decode row
     uint32_t max_seqs() const { return max_seqs_; }
     uint32_t max_blocks() const { return max_blocks_; }
     uint32_t n_blocks() const { return n_blocks_; }

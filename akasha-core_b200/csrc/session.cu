@@ -15,6 +15,14 @@ struct ak_session {
     bool has_cache = false;  // `cache: Option<Cache>` (src/nn/inference.rs:18)
     uint32_t cur_len = 0;    // Cache::cur_len (src/nn/inference_graphs.rs:515)
     Runner runner;
+    // sampled generation: the history (prompt + generated ids) on the device for the repetition penalty
+    uint32_t* d_hist = nullptr;
+    uint32_t* d_hist_off = nullptr;   // {0, history length}
+    uint32_t hist_cap = 0;
+    ~ak_session() {
+        if (d_hist) cudaFree(d_hist);
+        if (d_hist_off) cudaFree(d_hist_off);
+    }
 };
 
 static void fill_identity_table(ak_session* s) {
@@ -155,6 +163,66 @@ int ak_session_generate_greedy(ak_session* s, const uint32_t* prompt, uint32_t n
         rc = s->runner.sync();
         if (rc) return rc;
         next = s->runner.h_sampled()[0];
+    }
+    return AK_OK;
+}
+
+// src/nn/inference.rs:264-326 with sample_token (src/nn/sampling.rs:18-81) on the device.
+int ak_session_generate(ak_session* s, const uint32_t* prompt, uint32_t n, uint32_t max_new, float temperature, uint32_t top_k,
+                        float top_p, float repetition_penalty, uint64_t seed, int stop_on_eos, uint32_t* out_tokens, uint32_t* n_out) {
+    AK_REQUIRE(s && n_out, AK_ERR_INVALID_ARG, "ak_session_generate: null pointer");
+    *n_out = 0;
+    AK_REQUIRE(n != 0, AK_EMPTY_PROMPT, "prompt is empty");
+    AK_REQUIRE(prompt && (out_tokens || max_new == 0), AK_ERR_INVALID_ARG, "ak_session_generate: null pointer");
+    cudaStream_t st = s->ctx->stream;
+    AK_CUDA(cudaSetDevice(s->ctx->device));
+    if (!s->has_cache) {
+        s->has_cache = true;
+        s->cur_len = 0;
+    }
+    // history = prompt, then every generated id (sample_token's `seen`, src/nn/inference.rs:303-317)
+    const uint32_t need = n + max_new + 1;
+    if (s->hist_cap < need) {
+        if (s->d_hist) cudaFree(s->d_hist);
+        s->d_hist = nullptr;
+        s->hist_cap = 0;
+        AK_CUDA(cudaMalloc((void**)&s->d_hist, (size_t)need * 4));
+        s->hist_cap = need;
+    }
+    if (!s->d_hist_off) AK_CUDA(cudaMalloc((void**)&s->d_hist_off, 8));
+    AK_CUDA(cudaMemcpyAsync(s->d_hist, prompt, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    uint32_t next = 0;
+    int rc;
+    if (s->cur_len == 0) {
+        rc = ak_session_prefill(s, prompt, n, nullptr, &next);
+        if (rc) return rc;
+    } else {
+        for (uint32_t i = 0; i < n; i++) {
+            rc = ak_session_decode_step(s, prompt[i], nullptr, &next);
+            if (rc) return rc;
+        }
+    }
+    Runner& r = s->runner;
+    const uint32_t V = s->w->cfg.vocab_size, eos = s->w->cfg.eos_token;
+    uint32_t hist_len = n;
+    for (uint32_t i = 0; i < max_new; i++) {
+        // sample from the logits of the step just run; the id replaces the greedy one the step left for the next decode row
+        const uint32_t off[2] = {0u, hist_len};
+        AK_CUDA(cudaMemcpyAsync(s->d_hist_off, off, 8, cudaMemcpyHostToDevice, st));
+        rc = launch_sample_rows(st, r.logits_dev(), 1, V, r.logits_ld(), s->d_hist, s->d_hist_off, repetition_penalty, temperature, top_k,
+                                top_p, seed, i, nullptr, r.sampled_dev());
+        if (rc) return rc;
+        AK_CUDA(cudaMemcpyAsync(s->d_hist + hist_len, r.sampled_dev(), 4, cudaMemcpyDeviceToDevice, st));
+        AK_CUDA(cudaMemcpyAsync(&next, r.sampled_dev(), 4, cudaMemcpyDeviceToHost, st));
+        AK_CUDA(cudaStreamSynchronize(st));
+        hist_len++;
+        out_tokens[(*n_out)++] = next;
+        if (stop_on_eos && next == eos) break;
+        if (s->cur_len >= s->max_ctx) break;  // out of context mid-generation: return what we have
+        rc = decode_one(s, -1);               // the sampled id is read on the device
+        if (rc) return rc;
+        rc = r.sync();
+        if (rc) return rc;
     }
     return AK_OK;
 }

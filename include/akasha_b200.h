@@ -150,7 +150,9 @@ AK_API int ak_argmax(void* stream, const float* logits, uint32_t rows, uint32_t 
 /* sampling::sample_token (src/nn/sampling.rs:18-81) on the device, one row per sequence:
  * repetition penalty over the DISTINCT ids of seen[seen_off[r] .. seen_off[r+1]) (positive logits
  * divided, the others multiplied), then temperature / top-k / top-p with f64 probabilities.
- * temperature <= 0 is greedy. top_k must be 1..1024 when sampling. The uniform draw is
+ * temperature <= 0 is greedy. top_k when sampling: 1..1024, or 0 (or >= n) = no truncation, the reference's
+ * default (the candidate list is the whole row; the top-p cut and the draw are located by bisection on the logit
+ * value instead of a 50k-element sort). The uniform draw is
  * splitmix64(seed, step, row) (the reference uses an unseeded generator); equal logits are ordered
  * by index (the reference's unstable sort leaves that order open). */
 AK_API int ak_sample_token(void* stream, const float* logits, uint32_t rows, uint32_t n, const uint32_t* seen,
@@ -330,6 +332,15 @@ AK_API int ak_session_decode_step(ak_session* s, uint32_t token, float* logits_o
  * stop_on_eos != 0, and stops quietly when the context fills. Token ids only cross PCIe. */
 AK_API int ak_session_generate_greedy(ak_session* s, const uint32_t* prompt, uint32_t n, uint32_t max_new,
                                       int stop_on_eos, uint32_t* out_tokens, uint32_t* n_out);
+/* generate (src/nn/inference.rs:264-326) with the reference's sampler on the device: every step's logits stay in
+ * HBM, `sample_token` (src/nn/sampling.rs:18-81: repetition penalty over prompt + generated ids, temperature,
+ * top-k, top-p, one uniform draw) runs as a kernel on them, and only the chosen id crosses PCIe. `run_chat` calls
+ * it with (0.8, 40, 0.95, 1.15) (src/main.rs:160-162). temperature <= 0 is greedy over the penalised logits.
+ * The draw of generated token t is the counter-based uniform number of (seed, t, row 0) that ak_sample_token
+ * documents (the reference's generator is unseeded). top_k: 1..1024, or 0 = no truncation. */
+AK_API int ak_session_generate(ak_session* s, const uint32_t* prompt, uint32_t n, uint32_t max_new, float temperature,
+                               uint32_t top_k, float top_p, float repetition_penalty, uint64_t seed, int stop_on_eos,
+                               uint32_t* out_tokens, uint32_t* n_out);
 /* Copy the cached K (post-RoPE) and V rows 0..cur_len-1 of one layer to host as f32
  * [cur_len, dim] in the reference's contiguous layout (src/nn/inference_graphs.rs:511-543). */
 AK_API int ak_session_read_cache(ak_session* s, uint32_t layer, float* k_out, float* v_out);
