@@ -118,6 +118,7 @@ _PROTOS = {
     "ak_rope_kv_append": [vp, vp, vp, vp, vp, vp, vp] + [C.c_uint32] * 5,
     "ak_rmsnorm_rope_residual": [vp, vp, vp, vp, vp, vp, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32, C.c_uint32],
     "ak_gemm_bf16": [vp, vp, vp, vp, MatMulMeta, C.c_uint32],
+    "ak_gemm_bf16_ld": [vp, vp, vp, vp, MatMulMeta, C.c_uint32, C.c_uint32],
     "ak_transpose_to_bf16": [vp, vp, vp, C.c_uint32, C.c_uint32],
     "ak_f32_to_bf16": [vp, vp, vp, C.c_uint64],
     "ak_bf16_to_f32": [vp, vp, vp, C.c_uint64],

@@ -688,3 +688,8 @@ extern "C" int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c
     AK_REQUIRE(a && wt && c, AK_ERR_INVALID_ARG, "ak_gemm_bf16: null pointer");
     return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, m.n, false);
 }
+extern "C" int ak_gemm_bf16_ld(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue, uint32_t ldc) {
+    AK_REQUIRE(a && wt && c, AK_ERR_INVALID_ARG, "ak_gemm_bf16_ld: null pointer");
+    AK_REQUIRE(ldc >= m.n, AK_ERR_INVALID_ARG, "ak_gemm_bf16_ld: ldc (%u) must be at least n (%u)", ldc, m.n);
+    return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, ldc, false);
+}

@@ -160,8 +160,12 @@ def rmsnorm_rope_residual(x, residual, weight, y, positions, rows, size, eps=1e-
                                          size, eps, head_dim, out_dtype))
 
 
-def gemm_bf16(a, wt, c, m, n, k, epilogue=0, stream=None):
-    check(lib().ak_gemm_bf16(_s(stream), _p(a), _p(wt), _p(c), MatMulMeta(m, n, k), epilogue))
+def gemm_bf16(a, wt, c, m, n, k, epilogue=0, stream=None, ldc=0):
+    """C[m,n] (op)= A[m,k] @ Wt[n,k]^T on the tensor cores; `ldc` = row pitch of C in elements (0 = n)."""
+    if ldc:
+        check(lib().ak_gemm_bf16_ld(_s(stream), _p(a), _p(wt), _p(c), MatMulMeta(m, n, k), epilogue, ldc))
+    else:
+        check(lib().ak_gemm_bf16(_s(stream), _p(a), _p(wt), _p(c), MatMulMeta(m, n, k), epilogue))
 
 
 def transpose_to_bf16(w_kn, wt_nk, k, n, stream=None):

@@ -258,6 +258,10 @@ typedef enum ak_gemm_epilogue {
     AK_EPI_SILU_BF16 = 3   /* C bf16 = silu(acc)              (matmul + silu)     */
 } ak_gemm_epilogue;
 AK_API int ak_gemm_bf16(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue);
+/* The same with an explicit row pitch of C, in elements (ldc >= n). The epilogue writes 16- and 32-byte vectors
+ * when the pitch is a multiple of 8 elements and falls back to element stores otherwise, so an output with an odd
+ * width (n = 50257, the lm_head) should be given a padded pitch (50264): the odd pitch costs ~7x in store time. */
+AK_API int ak_gemm_bf16_ld(void* stream, const void* a, const void* wt, void* c, ak_matmul_meta m, uint32_t epilogue, uint32_t ldc);
 
 /* Make the [n,k] bf16 operand from a reference-layout f32 [k,n] matrix (device to device). */
 AK_API int ak_transpose_to_bf16(void* stream, const float* w_kn, void* wt_nk, uint32_t k, uint32_t n);

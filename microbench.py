@@ -102,12 +102,13 @@ def bench_gemm(ak, torch, iters, small):
     for N in (2304, 3072, 50257):
         a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
         wt = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
-        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        fn = lambda: ak.ops.gemm_bf16(a, wt, c, M, N, K, ak.EPI_STORE_BF16, stream)
+        ldc = (N + 7) // 8 * 8      # a row pitch of whole 16-byte vectors (50257 -> 50264)
+        c = torch.empty(M, ldc, device="cuda", dtype=torch.bfloat16)
+        fn = lambda: ak.ops.gemm_bf16(a, wt, c, M, N, K, ak.EPI_STORE_BF16, stream, ldc=ldc)
         ms = timed(torch, fn, max(3, iters // (8 if N > 10000 else 1)))
         fl = 2.0 * M * N * K
         t = fl / (ms * 1e-3) / 1e12
-        res.append({"kernel": "gemm_bf16_kernel (tcgen05)", "m": M, "n": N, "k": K, "ms": ms, "TFLOP/s": t,
+        res.append({"kernel": "gemm_bf16_kernel (tcgen05)", "m": M, "n": N, "k": K, "ldc": ldc, "ms": ms, "TFLOP/s": t,
                     "peak_TFLOP/s": tf, "frac": t / tf, "peak_source": src})
         del a, wt, c
     return res
