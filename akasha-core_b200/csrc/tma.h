@@ -25,11 +25,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
         "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
         : "memory");
 }
-// Bring a tile into L2 only (no shared-memory destination, no completion to wait for): lets a kernel put its whole
-// HBM stream in flight at once and run its shared-memory ring against L2 latency afterwards. Same alignment rule for x.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int32_t x, int32_t y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
-}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
