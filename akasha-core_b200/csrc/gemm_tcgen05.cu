@@ -457,6 +457,238 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------
+// CTA-pair kernel for large m: tcgen05.mma.cta_group::2, persistent, double-buffered accumulators.
+//
+// A cluster of two CTAs (on the two SMs of a TPC; one CTA per SM, one pair per SM pair) walks over [256 x BN] output
+// tiles. Each CTA stages ITS 128 rows of A and ITS half (BN/2 rows) of the weight tile per K block; the even CTA (the
+// leader) issues one MMA of shape 256 x BN x 16 that reads both CTAs' shared memory and accumulates rows 0-127 into
+// the leader's TMEM and rows 128-255 into the peer's. Per SM and K block that is 16 KB of A + BN/4 KB of B for a
+// 128 x BN slice of output: half the weight traffic from L2 per flop of the one-CTA kernel, which is what bounds that
+// kernel. The 512 TMEM columns hold TWO accumulator buffers: the epilogue warps drain tile i while the MMAs of tile
+// i+1 run, so no second CTA per SM is needed to hide the epilogue and the ring can use the whole shared memory.
+// Synchronisation (every wait bounded):
+//   full[s]      leader's barrier; both CTAs' TMA loads (.cta_group::2, no multicast: each CTA fetches its own tiles)
+//                complete on it, the leader arms it with the bytes of both;
+//   empty[s]     one per CTA; after the MMAs of a K block the leader commits to its own and to the peer's
+//                (two plain tcgen05.commit, the peer's addressed through the cluster window);
+//   acc_full[b]  one per CTA, committed by the leader after a tile's last MMA;
+//   acc_empty[b] leader's barrier, 8 arrivals: one per epilogue warp of both CTAs (the peer's arrive remotely).
+// TMEM is allocated and freed with the .cta_group::2 forms by warp 1 of both CTAs, with cluster barriers after the
+// allocation and before the release.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_dst, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// arrive on the mbarrier at shared::cluster address `bar_cluster_addr` once every MMA issued so far has completed
+__device__ __forceinline__ void tc_commit2(uint32_t bar_cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tc_mma2_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// TMA tiled load of a CTA pair: the data lands in THIS CTA's shared memory, the bytes are counted on the mbarrier at
+// `bar_cluster_addr`, which may live in the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, int32_t x, int32_t y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+template <int BN> struct PairCfg {
+    static constexpr int A_BYTES = GB_M * GB_K * 2;          // this CTA's 128 rows of A: 16 KB
+    static constexpr int B_BYTES = (BN / 2) * GB_K * 2;      // this CTA's half of the weight tile
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 512;                    // two accumulator buffers of kseg * BN columns
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(G_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmEpi ep,
+                      uint32_t m, uint32_t n, uint32_t k, uint32_t stages, uint32_t kseg, uint32_t tiles_n, uint32_t tiles_total) {
+    using C = PairCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[G_MAX_STAGES], empty_bar[G_MAX_STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_sm;
+    __shared__ uint32_t fail_flag;
+
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
+    const uint32_t pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const uint32_t num_kb = (k + GB_K - 1) / GB_K;
+    const uint32_t buf_cols = kseg * BN;
+    // two accumulator buffers when they fit the 512 columns (the epilogue of a tile then runs under the next tile's
+    // MMAs), else one (K split in two segments of 256 columns each: the epilogue is exposed)
+    const uint32_t n_bufs = (2 * buf_cols <= (uint32_t)C::TMEM_COLS) ? 2u : 1u;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < stages; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (uint32_t b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        fail_flag = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (warp == 1) {
+        tmem_alloc2(&tmem_base_sm, C::TMEM_COLS);
+        tmem_relinquish2();
+    }
+    tc_fence_before();
+    __syncthreads();
+    // both CTAs hold their TMEM columns and have initialised their barriers before either touches the other's
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_sm;
+    pdl_trigger();   // only after the TMEM allocation (see the one-CTA kernel)
+
+    if (warp == 0) {
+        // ---------------- TMA producer (one per CTA; bytes are counted on the leader's full barriers)
+        if (lane == 0) {
+            pdl_wait();
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t t = pair; t < tiles_total && ok; t += n_pairs) {
+                const uint32_t m0 = ((t / tiles_n) * 2 + rank) * GB_M;        // this CTA's 128 rows of the pair's 256
+                const uint32_t nb0 = (t % tiles_n) * BN + rank * (BN / 2);    // this CTA's half of the weight rows
+                for (uint32_t kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                    if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); ok = false; break; }
+                    uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
+                    const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+                    if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * C::STAGE_BYTES);
+                    const int32_t kx = (int32_t)(kb * GB_K);
+                    tma_load_2d_pair(a_dst, &tmA, kx, (int32_t)m0, bar);
+                    tma_load_2d_pair(a_dst + C::A_BYTES, &tmB, kx, (int32_t)nb0, bar);
+                }
+            }
+            // drain: every commit the leader addressed to this CTA's empty barriers has landed before the CTA may leave
+            for (uint32_t j = (it > stages ? it - stages : 0); j < it && ok; j++)
+                if (!mbar_wait(&empty_bar[j % stages], (j / stages) & 1u)) { atomicExch(&fail_flag, 5u); break; }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer: one thread of the leader CTA drives both SMs' tensor cores
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc(2 * GB_M, BN);
+            const uint32_t per_seg = (num_kb + kseg - 1) / kseg;
+            uint32_t it = 0, tc = 0;
+            bool ok = true;
+            for (uint32_t t = pair; t < tiles_total && ok; t += n_pairs, tc++) {
+                const uint32_t buf = n_bufs == 2 ? (tc & 1u) : 0u, acc_ph = (n_bufs == 2 ? (tc >> 1) : tc) & 1u;
+                // the epilogue warps of both CTAs have drained this buffer (it was last used by tile tc - n_bufs)
+                if (tc >= n_bufs && !mbar_wait(&acc_empty[buf], acc_ph ^ 1u)) { atomicExch(&fail_flag, 4u); break; }
+                tc_fence_after();
+                for (uint32_t kb = 0; kb < num_kb; kb++, it++) {
+                    const uint32_t seg = kb / per_seg, first_of_seg = (kb - seg * per_seg) == 0;
+                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                    if (!mbar_wait(&full_bar[s], ph)) { atomicExch(&fail_flag, 2u); ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + C::A_BYTES);
+#pragma unroll
+                    for (uint32_t kk = 0; kk < GB_K / 16; kk++)
+                        tc_mma2_f16(tmem_base + buf * buf_cols + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
+                                    (first_of_seg && kk == 0) ? 0u : 1u);
+                    // the stage is reusable in BOTH CTAs once these MMAs have read it
+                    tc_commit2(map_to_cta(smem_u32(&empty_bar[s]), 0));
+                    tc_commit2(map_to_cta(smem_u32(&empty_bar[s]), 1));
+                }
+                if (!ok) break;
+                tc_commit2(map_to_cta(smem_u32(&acc_full[buf]), 0));
+                tc_commit2(map_to_cta(smem_u32(&acc_full[buf]), 1));
+            }
+        }
+    } else {
+        // ---------------- epilogue warps 2..5 of both CTAs: thread <-> accumulator row of THIS CTA's TMEM
+        const uint32_t quad = warp & 3u;
+        pdl_wait();
+        uint32_t tc = 0;
+        for (uint32_t t = pair; t < tiles_total; t += n_pairs, tc++) {
+            const uint32_t buf = n_bufs == 2 ? (tc & 1u) : 0u, acc_ph = (n_bufs == 2 ? (tc >> 1) : tc) & 1u;
+            const uint32_t row = ((t / tiles_n) * 2 + rank) * GB_M + quad * 32 + lane;
+            const uint32_t n0 = (t % tiles_n) * BN;
+            bool got = num_kb == 0 || mbar_wait(&acc_full[buf], acc_ph);
+            if (!got && lane == 0) atomicExch(&fail_flag, 3u);
+            got = __all_sync(0xffffffffu, got);
+            if (!got) break;
+            tc_fence_after();
+            float best = -INFINITY;
+            uint32_t best_i = 0xffffffffu;
+#pragma unroll 1
+            for (uint32_t c0 = 0; c0 < (uint32_t)BN; c0 += 16) {
+                uint32_t r[16];
+                float v[16];
+                if (num_kb > 0) {
+                    tmem_ld16(tmem_base + ((quad * 32u) << 16) + buf * buf_cols + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = __uint_as_float(r[j]);
+                    for (uint32_t seg = 1; seg < kseg; seg++) {
+                        tmem_ld16(tmem_base + ((quad * 32u) << 16) + buf * buf_cols + seg * BN + c0, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++) v[j] += __uint_as_float(r[j]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] = 0.0f;
+                }
+                if (EPI != EPI_ARGMAX) epi_store16<EPI>(ep, row, row < m, n0 + c0, v, n, lane);
+                if (row < m && (EPI == EPI_ARGMAX || EPI == EPI_STORE_F32_ARGMAX)) {
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        if (n0 + c0 + j < n && v[j] > best) { best = v[j]; best_i = n0 + c0 + j; }
+                }
+            }
+            if ((EPI == EPI_ARGMAX || EPI == EPI_STORE_F32_ARGMAX) && row < m) {
+                ep.amax_val[(size_t)row * ep.amax_ld + (t % tiles_n)] = best;
+                ep.amax_idx[(size_t)row * ep.amax_ld + (t % tiles_n)] = best_i;
+            }
+            // this warp has read its part of the buffer: let the leader's MMA thread reuse it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        }
+    }
+    // ---------------- common exit: nobody frees TMEM or leaves while the pair may still use this CTA's memory
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && fail_flag) atomicExch(&g_gemm_status, fail_flag);
+    cluster_sync_all();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc2(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Launch configuration.
 struct GemmPlan {
     uint32_t bn, ks, stages;
@@ -492,8 +724,11 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
                 // decode plan, with the widest tile that still fits one wave of two CTAs per SM.
                 p.ks = sk.ks;
                 p.bn = 16;
+#ifndef AK_MIDM_FIRST
+#define AK_MIDM_FIRST 0
+#endif
                 const uint32_t cands[3] = {64, 32, 16};
-                for (int i = 0; i < 3; i++)
+                for (int i = AK_MIDM_FIRST; i < 3; i++)
                     if ((cands[i] / p.ks) % 4 == 0 && (uint64_t)mt * cdiv(n, cands[i]) * p.ks <= 296) { p.bn = cands[i]; break; }
                 if ((p.bn / p.ks) % 4 != 0) p.bn = 4 * p.ks;  // 16 or 32: always a legal tile width
                 const uint32_t per = cdiv(num_kb, p.ks);
@@ -633,6 +868,58 @@ static int launch_planned(cudaStream_t st, const void* a, const void* wt, const 
     }
 }
 
+// ---- the CTA-pair kernel's launch
+template <int BN, int EPI>
+static int launch_pair_cfg(cudaStream_t st, const void* a, const void* wt, const GemmEpi& ep, uint32_t m, uint32_t n, uint32_t k, uint32_t kseg) {
+    using C = PairCfg<BN>;
+    uint32_t stages = (SMEM_ONE_PER_SM - 1024) / C::STAGE_BYTES;
+    if (stages > G_MAX_STAGES) stages = G_MAX_STAGES;
+    const size_t smem = (size_t)stages * C::STAGE_BYTES + 1024;
+    {
+        static bool attr_set[64] = {};
+        int dev = 0;
+        AK_CUDA(cudaGetDevice(&dev));
+        std::lock_guard<std::mutex> lock(device_cache_mutex());
+        if (!attr_set[dev & 63]) {
+            AK_CUDA(cudaFuncSetAttribute(gemm_bf16_pair_kernel<BN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ONE_PER_SM));
+            attr_set[dev & 63] = true;
+        }
+    }
+    CUtensorMap tmA, tmB;
+    AK_TRY(make_tmap_2d(&tmA, a, 2, k, m, (uint64_t)k * 2, GB_K, GB_M, TMA_SWIZZLE_128B));
+    AK_TRY(make_tmap_2d(&tmB, wt, 2, k, n, (uint64_t)k * 2, GB_K, BN / 2, TMA_SWIZZLE_128B));
+    const uint32_t tiles_n = cdiv(n, BN), tiles_total = tiles_n * cdiv(m, 2 * GB_M);
+    const uint32_t n_pairs = tiles_total < 74 ? tiles_total : 74;   // one pair per TPC of the 148 SMs
+    return launch_k(gemm_bf16_pair_kernel<BN, EPI>, dim3(2 * n_pairs, 1, 1), dim3(G_THREADS), smem, st, dim3(2, 1, 1), tmA, tmB, ep, m, n, k,
+                    stages, kseg, tiles_n, tiles_total);
+}
+template <int BN>
+static int launch_pair(cudaStream_t st, const void* a, const void* wt, const GemmEpi& ep, uint32_t m, uint32_t n, uint32_t k, uint32_t epi,
+                       uint32_t kseg) {
+    switch (epi) {
+        case AK_EPI_STORE_F32: return launch_pair_cfg<BN, AK_EPI_STORE_F32>(st, a, wt, ep, m, n, k, kseg);
+        case AK_EPI_ADD_F32: return launch_pair_cfg<BN, AK_EPI_ADD_F32>(st, a, wt, ep, m, n, k, kseg);
+        case AK_EPI_STORE_BF16: return launch_pair_cfg<BN, AK_EPI_STORE_BF16>(st, a, wt, ep, m, n, k, kseg);
+        case AK_EPI_SILU_BF16: return launch_pair_cfg<BN, AK_EPI_SILU_BF16>(st, a, wt, ep, m, n, k, kseg);
+    }
+    set_error("gemm_bf16: unknown epilogue %u", epi);
+    return AK_ERR_INVALID_ARG;
+}
+// Large m goes to the CTA-pair kernel when the accumulators of its K partition fit TMEM: one accumulator of 256
+// columns (no K split for this (n, k): two buffers, epilogue overlapped), or two of 256 (the skinny plan splits K
+// two ways: one buffer).
+static bool pair_plan(uint32_t m, uint32_t n, uint32_t k, bool allow_split, bool invariant, uint32_t& bn, uint32_t& kseg) {
+    if (m < 1024 || n < 256) return false;
+    kseg = 1;
+    if (invariant && allow_split) {
+        const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
+        if (sk.ks > 2) return false;   // more than 512 accumulator columns at 256 per segment
+        kseg = sk.ks;
+    }
+    bn = 256;
+    return true;
+}
+
 static int check_operands(const void* a, const void* wt, uint32_t k) {
     AK_REQUIRE(k >= 8 && k % 8 == 0, AK_ERR_UNSUPPORTED, "gemm_bf16: k (%u) must be a positive multiple of 8", k);
     AK_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)wt % 16) == 0, AK_ERR_INVALID_ARG, "gemm_bf16: operands must be 16-byte aligned");
@@ -651,6 +938,8 @@ int launch_gemm_bf16(cudaStream_t st, const void* a, const void* wt, void* c, ui
     ep.ldc = ldc ? ldc : n;
     // the split-K exchange stores 4-column groups: it needs 4-aligned rows
     const bool allow_split = (ep.ldc % 4) == 0;
+    uint32_t pbn = 0, pkseg = 1;
+    if (pair_plan(m, n, k, allow_split, invariant, pbn, pkseg)) return launch_pair<256>(st, a, wt, ep, m, n, k, epilogue, pkseg);
     return launch_planned(st, a, wt, ep, m, n, k, epilogue, plan_gemm(m, n, k, allow_split, invariant));
 }
 
