@@ -724,11 +724,8 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
                 // decode plan, with the widest tile that still fits one wave of two CTAs per SM.
                 p.ks = sk.ks;
                 p.bn = 16;
-#ifndef AK_MIDM_FIRST
-#define AK_MIDM_FIRST 0
-#endif
-                const uint32_t cands[3] = {64, 32, 16};
-                for (int i = AK_MIDM_FIRST; i < 3; i++)
+                const uint32_t cands[3] = {64, 32, 16};   // measured: starting from 32 or 16 is slower (1.23 / 1.28 ms against 1.14)
+                for (int i = 0; i < 3; i++)
                     if ((cands[i] / p.ks) % 4 == 0 && (uint64_t)mt * cdiv(n, cands[i]) * p.ks <= 296) { p.bn = cands[i]; break; }
                 if ((p.bn / p.ks) % 4 != 0) p.bn = 4 * p.ks;  // 16 or 32: always a legal tile width
                 const uint32_t per = cdiv(num_kb, p.ks);
@@ -905,16 +902,17 @@ static int launch_pair(cudaStream_t st, const void* a, const void* wt, const Gem
     set_error("gemm_bf16: unknown epilogue %u", epi);
     return AK_ERR_INVALID_ARG;
 }
-// Large m goes to the CTA-pair kernel when the accumulators of its K partition fit TMEM: one accumulator of 256
-// columns (no K split for this (n, k): two buffers, epilogue overlapped), or two of 256 (the skinny plan splits K
-// two ways: one buffer).
+// Large m goes to the CTA-pair kernel when its K partition is a single accumulator of 256 columns (two TMEM
+// buffers, the epilogue of a tile overlapped with the next tile's MMAs).
 static bool pair_plan(uint32_t m, uint32_t n, uint32_t k, bool allow_split, bool invariant, uint32_t& bn, uint32_t& kseg) {
     if (m < 1024 || n < 256) return false;
     kseg = 1;
     if (invariant && allow_split) {
+        // With K split in two segments of 256 columns the accumulators fill TMEM, the epilogue is exposed and the
+        // kernel is no faster than the one-CTA kernel (measured on the 1.4B prefill: 12.0 s against 11.9 s): only
+        // unsplit K partitions go to the pair kernel. (The kernel itself handles kseg = 2 with a single buffer.)
         const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
-        if (sk.ks > 2) return false;   // more than 512 accumulator columns at 256 per segment
-        kseg = sk.ks;
+        if (sk.ks > 1) return false;
     }
     bn = 256;
     return true;
