@@ -65,7 +65,7 @@ FlashAttnMeta = _u32struct("FlashAttnMeta", ["seq_len", "dim", "head_dim", "scal
 AttnDecodeParams = _u32struct("AttnDecodeParams", ["rows", "heads", "head_dim", "block_size", "max_blocks_per_seq",
                                                    "scale", "kv_dtype", "n_splits", "pool_blocks"], floats=("scale",))
 EngineConfig = _u32struct("EngineConfig", ["max_seqs", "max_seq_len", "kv_blocks", "block_size", "max_batch_tokens",
-                                           "use_cuda_graph", "stop_on_eos", "attn_timing", "async_steps", "detached_prefill"])
+                                           "use_cuda_graph", "stop_on_eos", "attn_timing", "async_steps", "prefill_chunk_rows"])
 
 
 class EngineStats(C.Structure):
@@ -491,10 +491,10 @@ class Engine:
 
     def __init__(self, ctx: Context, weights: ModelWeights, max_seqs: int, max_seq_len: int, kv_blocks: int = 0,
                  max_batch_tokens: int = 0, use_cuda_graph: bool = True, stop_on_eos: bool = False,
-                 attn_timing: bool = False, async_steps: bool = False, detached_prefill: bool = False):
+                 attn_timing: bool = False, async_steps: bool = False, prefill_chunk_rows: int = 0):
         self.ctx, self.weights = ctx, weights
         cfg = EngineConfig(max_seqs, max_seq_len, kv_blocks, 16, max_batch_tokens, int(use_cuda_graph),
-                           int(stop_on_eos), int(attn_timing), int(async_steps), int(detached_prefill))
+                           int(stop_on_eos), int(attn_timing), int(async_steps), int(prefill_chunk_rows))
         self.h = vp()
         check(lib().ak_engine_create(ctx.h, weights.h, C.byref(cfg), C.byref(self.h)))
 

@@ -299,14 +299,14 @@ static int launch_generic(cudaStream_t st, const T* q, const T* k, const T* v, c
 
 int launch_attn_prefill_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                               const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
-                              const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base,
+                              const int32_t* seq_slot, const int32_t* pos0, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base,
                               uint32_t heads, uint32_t head_dim, uint32_t block_size, float scale, uint32_t dtype,
                               uint64_t q_rows, uint64_t pool_blocks) {
     if (n_seqs == 0 || max_len == 0) return AK_OK;
     AK_REQUIRE(block_size == PF_BS, AK_ERR_UNSUPPORTED, "prefill attention: block_size must be 16");
     // bf16 with a tensor-core friendly head size: the tcgen05 kernel (needs the extents for its tensor maps)
     if (dtype == AK_BF16 && (head_dim == 64 || head_dim == 128) && q_rows && pool_blocks)
-        return launch_attn_prefill_tc(st, q, q_rows, k_pool, v_pool, pool_blocks, block_tables, max_blocks_per_seq, cu, seq_slot, out,
+        return launch_attn_prefill_tc(st, q, q_rows, k_pool, v_pool, pool_blocks, block_tables, max_blocks_per_seq, cu, seq_slot, pos0, out,
                                       n_seqs, max_len, row_base, heads, head_dim, scale);
     if (dtype == AK_F32) {
         auto Q = (const float*)q; auto K = (const float*)k_pool; auto V = (const float*)v_pool; auto O = (float*)out;
@@ -349,6 +349,6 @@ extern "C" int ak_attn_prefill_paged(void* stream, const void* q, const void* k_
     AK_REQUIRE(q && k_pool && v_pool && block_tables && cu && seq_slot && out, AK_ERR_INVALID_ARG, "ak_attn_prefill_paged: null pointer");
     AK_REQUIRE(dtype == AK_F32 || dtype == AK_BF16, AK_ERR_INVALID_ARG, "ak_attn_prefill_paged: dtype must be f32 or bf16");
     AK_REQUIRE(heads >= 1 && head_dim >= 1, AK_ERR_INVALID_ARG, "ak_attn_prefill_paged: empty head shape");
-    return launch_attn_prefill_paged(as_stream(stream), q, k_pool, v_pool, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs,
+    return launch_attn_prefill_paged(as_stream(stream), q, k_pool, v_pool, block_tables, max_blocks_per_seq, cu, seq_slot, nullptr, out, n_seqs,
                                      max_len, 0, heads, head_dim, 16, scale, dtype, q_rows, pool_blocks);
 }

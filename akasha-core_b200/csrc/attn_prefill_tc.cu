@@ -96,8 +96,8 @@ template <int HD, int BKV>
 __global__ void __launch_bounds__(THREADS)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const int32_t* __restrict__ block_tables, uint32_t max_blocks,
-                  const int32_t* __restrict__ cu, const int32_t* __restrict__ seq_slot, bf16* __restrict__ out, uint32_t row_base,
-                  uint32_t heads, float scale) {
+                  const int32_t* __restrict__ cu, const int32_t* __restrict__ seq_slot, const int32_t* __restrict__ q_pos0,
+                  bf16* __restrict__ out, uint32_t row_base, uint32_t heads, float scale) {
     using C = Cfg<HD, BKV>;
     pdl_wait();
     extern __shared__ uint8_t smem_raw[];
@@ -105,7 +105,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     __shared__ uint32_t tmem_base_sm, fail_flag;
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BQ;
+    // len query rows at positions pos0 .. pos0 + len - 1 (pos0 > 0: a later chunk of a prompt whose first pos0
+    // positions are already in the cache); keys are positions 0 .. kv_len - 1
     const uint32_t len = (uint32_t)(cu[seq + 1] - cu[seq]);
+    const uint32_t pos0 = q_pos0 ? (uint32_t)q_pos0[seq] : 0u;
+    const uint32_t kv_len = pos0 + len;
     if (q0 >= len) { pdl_trigger(); return; }   // allocates no TMEM
     const uint32_t row0 = row_base + (uint32_t)cu[seq];
     const int32_t* table = block_tables + (size_t)seq_slot[seq] * max_blocks;
@@ -133,7 +137,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t tmem_s = tmem_base_sm, tmem_pv = tmem_base_sm + BKV;
     const uint32_t lane_addr = (warp * 32u) << 16;
 
-    const uint32_t q_hi = (q0 + BQ - 1 < len - 1) ? q0 + BQ - 1 : len - 1;
+    const uint32_t q_hi = pos0 + ((q0 + BQ - 1 < len - 1) ? q0 + BQ - 1 : len - 1);   // position of the tile's last query
     const uint32_t n_tiles = q_hi / BKV + 1;
 
     uint32_t loaded = 0, consumed = 0;  // thread 0: K/V tiles requested / waited for
@@ -146,7 +150,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         for (uint32_t blk = 0; blk < BKV / BS; blk++) {
             const uint32_t pos = t * BKV + blk * BS;
             // blocks past the sequence end are fetched from its first block: finite data, masked out below
-            const uint32_t bidx = pos < len ? pos / BS : 0;
+            const uint32_t bidx = pos < kv_len ? pos / BS : 0;
             const int32_t y = (int32_t)(((uint32_t)table[bidx] * heads + h) * BS);
 #pragma unroll
             for (int hf = 0; hf < C::HALVES; hf++) {
@@ -168,7 +172,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
     for (int d = 0; d < HD; d++) o[d] = 0.0f;
     float m_run = -INFINITY, l_run = 0.0f;
-    const uint32_t qi = q0 + tid;  // this thread's query position
+    const uint32_t qi = pos0 + q0 + tid;  // this thread's query position
     bool ok = true;
 
     for (uint32_t t = 0; t < n_tiles; t++) {
@@ -195,12 +199,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         if (!good) atomicExch(&fail_flag, 2u);
         tc_fence_after();
         const uint32_t k0 = t * BKV;
-        if (k0 + BKV > len) {
+        if (k0 + BKV > kv_len) {
             // Tile rows past the sequence end hold whatever the pool held (possibly non-finite): their
             // probabilities are 0, but 0 * NaN would poison P.V, so clear those V rows (whole 128-byte rows,
             // the swizzle permutes within a row only). Ordered before the MMA by the fence + barrier below.
             good = mbar_wait(&kv_bar[b], (t >> 1) & 1u) && good;
-            const uint32_t first = len - k0, chunks = (BKV - first) * 8;
+            const uint32_t first = kv_len - k0, chunks = (BKV - first) * 8;
             for (int hf = 0; hf < C::HALVES; hf++)
                 for (uint32_t i = tid; i < chunks; i += THREADS)
                     *reinterpret_cast<uint4*>(v_sm + hf * (BKV * 128) + (first + i / 8) * 128 + (i % 8) * 16) = make_uint4(0, 0, 0, 0);
@@ -215,7 +219,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
             for (int j = 0; j < 16; j++) {
                 const uint32_t kj = k0 + c0 + j;
-                if (kj <= qi && kj < len) mx = fmaxf(mx, __uint_as_float(r[j]) * scale);
+                if (kj <= qi && kj < kv_len) mx = fmaxf(mx, __uint_as_float(r[j]) * scale);
             }
         }
         const float m_new = fmaxf(m_run, mx);
@@ -234,7 +238,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
                     const uint32_t kj = k0 + c0 + j + e;
-                    const bool valid = kj <= qi && kj < len;
+                    const bool valid = kj <= qi && kj < kv_len;
                     p2[e] = valid ? __expf(__uint_as_float(r[j + e]) * scale - m_new) : 0.0f;
                 }
                 bf162 v2 = __floats2bfloat162_rn(p2[0], p2[1]);
@@ -279,9 +283,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
     if (!ok && tid == 0)  // leaving early: let the copies already requested land before the CTA's memory goes away
         for (uint32_t i = consumed; i < loaded; i++) mbar_wait(&kv_bar[i & 1], (i >> 1) & 1u);
-    if (ok && qi < len) {
+    if (ok && q0 + tid < len) {
         const float inv = 1.0f / l_run;
-        bf16* dst = out + (size_t)(row0 + qi) * dim + (size_t)h * HD;
+        bf16* dst = out + (size_t)(row0 + q0 + tid) * dim + (size_t)h * HD;
 #pragma unroll
         for (int d = 0; d < HD; d += 8) {
             uint32_t pk[4];
@@ -304,7 +308,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
 template <int HD, int BKV>
 static int launch(cudaStream_t st, const void* q, uint64_t q_rows, const void* k_pool, const void* v_pool, uint64_t pool_rows,
-                  const int32_t* bt, uint32_t max_blocks, const int32_t* cu, const int32_t* seq_slot, void* out, uint32_t n_seqs,
+                  const int32_t* bt, uint32_t max_blocks, const int32_t* cu, const int32_t* seq_slot, const int32_t* pos0, void* out, uint32_t n_seqs,
                   uint32_t max_len, uint32_t row_base, uint32_t heads, float scale) {
     using C = Cfg<HD, BKV>;
     CUtensorMap tmQ, tmK, tmV;
@@ -321,20 +325,20 @@ static int launch(cudaStream_t st, const void* q, uint64_t q_rows, const void* k
         attr_set[dev & 63] = true;
     }
     return launch_k(prefill_tc_kernel<HD, BKV>, dim3(cdiv(max_len, BQ), heads, n_seqs), dim3(THREADS), C::SMEM_BYTES, st, NO_CLUSTER, tmQ, tmK,
-                    tmV, bt, max_blocks, cu, seq_slot, (bf16*)out, row_base, heads, scale);
+                    tmV, bt, max_blocks, cu, seq_slot, pos0, (bf16*)out, row_base, heads, scale);
 }
 
 }  // namespace pftc
 
 int launch_attn_prefill_tc(cudaStream_t st, const void* q, uint64_t q_rows, const void* k_pool, const void* v_pool,
                            uint64_t pool_blocks, const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
-                           const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base, uint32_t heads,
+                           const int32_t* seq_slot, const int32_t* pos0, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base, uint32_t heads,
                            uint32_t head_dim, float scale) {
     if (n_seqs == 0 || max_len == 0) return AK_OK;
     const uint64_t pool_rows = pool_blocks * heads * pftc::BS;
     // keys per step: 128 for head_dim 64 (a little faster); 64 for head_dim 128, where 128 would leave room for
     // one CTA per SM only (measured slower on long prompts).
-#define AK_PF_ARGS st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, out, n_seqs, max_len, row_base, heads, scale
+#define AK_PF_ARGS st, q, q_rows, k_pool, v_pool, pool_rows, block_tables, max_blocks_per_seq, cu, seq_slot, pos0, out, n_seqs, max_len, row_base, heads, scale
     if (head_dim == 64) return pftc::launch<64, 128>(AK_PF_ARGS);
     AK_REQUIRE(head_dim == 128, AK_ERR_UNSUPPORTED, "prefill attention (tensor cores): head_dim must be 64 or 128");
     return pftc::launch<128, 64>(AK_PF_ARGS);

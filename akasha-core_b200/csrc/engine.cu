@@ -28,8 +28,8 @@ struct Seq {
     uint32_t cached = 0;  // tokens whose K/V are in the cache
     int slot = -1;
     bool finished = false;
-    bool prefilling = false;   // admitted, its prompt is running as a detached prefill
-    int32_t pf_last_row = -1;  // row of its last prompt token in the runner's activation buffers
+    bool in_prefill = false;   // admitted, its prompt is not fully in the cache yet
+    uint32_t prefilled = 0;    // prompt tokens already scheduled into the cache
 };
 
 }  // namespace
@@ -60,8 +60,8 @@ struct ak_engine {
     } pending;
     uint64_t weight_bytes = 0;   // bytes of every tensor a decode step reads in full (all but the embedding table)
     uint64_t step_index = 0;
-    bool pf_active = false;      // a detached prefill has been launched and has not joined yet
-    uint64_t pf_join_step = 0;   // the step in which its sequences sample their first token
+    std::deque<Seq*> prefill_queue;   // admitted sequences whose prompt is not fully scheduled, in admission order
+    uint32_t chunk_rows = 0;          // prompt rows per step while others decode (0 = whole prompts only)
     bool async_ok() const { return cfg.async_steps != 0 && cfg.stop_on_eos == 0; }
 };
 
@@ -135,6 +135,8 @@ int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak
         delete e;
         return rc;
     }
+    e->chunk_rows = e->runner.chunked_prefill_supported() ? cfg->prefill_chunk_rows : 0;
+    if (e->chunk_rows > e->runner.max_prefill_tokens()) e->chunk_rows = e->runner.max_prefill_tokens();
     e->runner.enable_attn_timing(cfg->attn_timing != 0);
     e->runner.set_keep_logits(false);
     for (const auto& pr : w->params)
@@ -190,21 +192,14 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     for (uint32_t i = 0; i < S; i++)
         if (e->slots[i] && e->slots[i]->finished) release(e, e->slots[i]);
 
-    // 2. admit waiting sequences in arrival order into the lowest free slots
-    std::vector<Seq*> admitted;
-    uint32_t pf_rows = 0;
-    const bool lag_ok = e->cfg.detached_prefill != 0 && e->cfg.use_cuda_graph != 0 && e->w->tp_size == 1;
-    const bool join_now = e->pf_active && e->step_index >= e->pf_join_step;
-    bool decoding_now = false;  // somebody is past its prompt: a new prompt can run beside the decode steps
-    for (uint32_t i = 0; i < S; i++) decoding_now |= (e->slots[i] && !e->slots[i]->finished && !e->slots[i]->prefilling);
-    while (!e->waiting.empty() && !(lag_ok && e->pf_active)) {
+    // 2. admit waiting sequences in arrival order into the lowest free slots; their prompts join the prefill queue
+    while (!e->waiting.empty()) {
         Seq* s = e->waiting.front();
         int slot = -1;
         for (uint32_t i = 0; i < S; i++)
             if (!e->slots[i]) { slot = (int)i; break; }
         const uint32_t need = (s->max_total + 15) / 16;
         if (slot < 0 || e->free_blocks.size() < need) break;
-        if (pf_rows + s->prompt.size() > r.max_prefill_tokens()) break;
         e->waiting.pop_front();
         s->slot = slot;
         e->slots[slot] = s;
@@ -214,17 +209,38 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
             s->blocks.push_back(*it);
             e->free_blocks.erase(it);
         }
-        pf_rows += (uint32_t)s->prompt.size();
-        admitted.push_back(s);
+        s->in_prefill = true;
+        s->prefilled = 0;
+        e->prefill_queue.push_back(s);
     }
 
-    const bool detach = lag_ok && !admitted.empty() && decoding_now;
-    if (detach) {
-        for (Seq* a : admitted) a->prefilling = true;
-        e->pf_active = true;
-        e->pf_join_step = e->step_index + 2;
+    // 3. choose the prompt rows of this step.
+    // Whole prompts (as many as fit the step budget) when nobody is decoding or a lot of prompt is pending. Otherwise
+    // chunks: while other sequences decode, a prompt is prefilled `chunk_rows` rows per step, so that decode rows and
+    // prompt rows together stay within ONE 128-row tile of every projection and the prompt rides in the decode
+    // launches; its sequence samples its first token in the step that holds its last chunk. Chunk boundaries depend on
+    // the prompt alone, and a row's arithmetic does not depend on which rows share its launch.
+    bool decoding_now = false;
+    for (uint32_t i = 0; i < S; i++) decoding_now |= (e->slots[i] && !e->slots[i]->finished && !e->slots[i]->in_prefill);
+    uint64_t pending_rows = 0;
+    for (Seq* s : e->prefill_queue) pending_rows += s->prompt.size() - s->prefilled;
+    const bool chunk_mode = e->chunk_rows > 0 && decoding_now && pending_rows > 0 && pending_rows <= 8ull * e->chunk_rows;
+    const uint32_t budget = chunk_mode ? e->chunk_rows : r.max_prefill_tokens();
+    struct Work { Seq* s; uint32_t c0, n; bool last; };
+    std::vector<Work> work;
+    uint32_t pf_rows = 0;
+    for (Seq* s : e->prefill_queue) {
+        const uint32_t left = (uint32_t)s->prompt.size() - s->prefilled;
+        uint32_t take = left;
+        if (chunk_mode) { if (take > budget - pf_rows) take = budget - pf_rows; }
+        else if (pf_rows + take > budget) break;     // whole prompts only: the next one waits for the next step
+        if (take == 0) break;
+        work.push_back({s, s->prefilled, take, take == left});
+        pf_rows += take;
+        if (pf_rows >= budget) break;
     }
-    // 3. describe the step: decode rows by slot, then the admitted prompts
+
+    // 4. describe the step: decode rows by slot, then the prompt rows
     RowInfo* rows = r.h_rows();
     int32_t* kv = r.h_kv_lens();
     int32_t* outr = r.h_out_rows();
@@ -235,15 +251,13 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     uint32_t n_dec = 0;
     for (uint32_t i = 0; i < S; i++) {
         Seq* s = e->slots[i];
-        bool is_new = false;
-        for (Seq* a : admitted) is_new |= (a == s);
         if (s && !s->finished) {
             // every bank of the descriptor carries its own copy of the tables: refresh the live ones
             int32_t* bt = r.h_block_table(i);
             const uint32_t nb = (uint32_t)s->blocks.size();
             for (uint32_t b = 0; b < r.max_blocks(); b++) bt[b] = b < nb ? s->blocks[b] : 0;
         }
-        if (s && !is_new && !s->finished && !s->prefilling) {
+        if (s && !s->finished && !s->in_prefill) {
             const uint32_t pos = s->cached;
             rows[i] = {-(int32_t)(i + 1), (int32_t)pos, s->blocks[pos / 16] * 16 + (int32_t)(pos % 16), (int32_t)i};
             kv[i] = (int32_t)(pos + 1);
@@ -256,29 +270,30 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         } else {
             rows[i] = {INT_MIN, -1, -1, (int32_t)i};
             kv[i] = 0;
-            // a detached prefill joins: its first token is sampled from its last prompt row in this step
-            outr[i] = (s && s->prefilling && join_now && !is_new) ? s->pf_last_row : -1;
+            outr[i] = -1;
         }
     }
     uint32_t row = S, max_pf = 0;
     int32_t* cu = r.h_pf_cu();
     int32_t* pfs = r.h_pf_slot();
+    int32_t* p0 = r.h_pf_pos0();
     cu[0] = 0;
-    for (size_t a = 0; a < admitted.size(); a++) {
-        Seq* s = admitted[a];
-        const uint32_t P = (uint32_t)s->prompt.size();
-        for (uint32_t j = 0; j < P; j++) {
-            uint32_t t = s->prompt[j];
-            rows[row + j] = {t > 0x7fffffffu ? INT_MAX : (int32_t)t, (int32_t)j, s->blocks[j / 16] * 16 + (int32_t)(j % 16), s->slot};
+    for (size_t a = 0; a < work.size(); a++) {
+        Seq* s = work[a].s;
+        const uint32_t c0 = work[a].c0, n = work[a].n;
+        for (uint32_t j = 0; j < n; j++) {
+            const uint32_t pos = c0 + j, t = s->prompt[pos];
+            rows[row + j] = {t > 0x7fffffffu ? INT_MAX : (int32_t)t, (int32_t)pos, s->blocks[pos / 16] * 16 + (int32_t)(pos % 16), s->slot};
         }
-        row += P;
+        row += n;
         cu[a + 1] = (int32_t)(row - S);
         pfs[a] = s->slot;
-        s->pf_last_row = (int32_t)(row - 1);
-        outr[s->slot] = detach ? -1 : (int32_t)(row - 1);
-        if (P > max_pf) max_pf = P;
+        p0[a] = (int32_t)c0;
+        // the sequence samples its first token from the last row of its last chunk
+        outr[s->slot] = work[a].last ? (int32_t)(row - 1) : -1;
+        if (n > max_pf) max_pf = n;
     }
-    if (!any_decode && admitted.empty() && !e->pf_active) {
+    if (!any_decode && work.empty()) {
         int rcf = collect(e);  // nothing to launch: make the last step's tokens visible
         if (rcf) return rcf;
         if (n_running) *n_running = 0;
@@ -286,53 +301,48 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
         return AK_OK;
     }
 
-    // 4. launch
+    // 5. launch
     int rc;
     const bool graph = e->cfg.use_cuda_graph != 0;
-    if (detach) {
-        rc = r.launch_prefill_detached(pf_rows, (uint32_t)admitted.size(), max_pf);
-        if (rc) return rc;
-        rc = r.run_graph(0, 0, 0);  // this step's decode rows, beside the prompt
-    } else {
-        if (join_now) { rc = r.join_prefill(); if (rc) return rc; }
-        if (graph) rc = r.run_graph(pf_rows, (uint32_t)admitted.size(), max_pf);
-        else rc = r.run(pf_rows, (uint32_t)admitted.size(), max_pf, any_decode, max_kv);
-    }
+    if (graph) rc = r.run_graph(pf_rows, (uint32_t)work.size(), max_pf);
+    else rc = r.run(pf_rows, (uint32_t)work.size(), max_pf, any_decode, max_kv);
     if (rc) return rc;
     rc = r.mark_done();
     if (rc) return rc;
 
-    // 5. advance the sequences by one token (the value is filled in when the step is collected)
+    // 6. advance the sequences (token values are filled in when the step is collected)
     ak_engine::Pending now;
     now.active = true;
     now.bank = r.bank();
     now.any_decode = any_decode;
-    now.has_prefill = pf_rows != 0 || r.prefill_in_flight();
+    now.has_prefill = pf_rows != 0;
     now.attn_bytes = attn_bytes;
     // per layer: the attention launch's bytes plus one appended K and V row per sequence; per step: the weights
     // and one embedding row per sequence
     now.step_bytes = e->weight_bytes + (uint64_t)n_dec * mc.dim * esz +
                      (uint64_t)mc.num_layers * (attn_bytes + (uint64_t)n_dec * 2 * r.local_qdim() * esz);
-    uint32_t running = 0;
+    auto emit_token = [&](Seq* s) {
+        now.fill.emplace_back(s, (uint32_t)s->generated.size());
+        now.fill_slot.push_back((uint32_t)s->slot);
+        s->generated.push_back(0);
+        if (s->prompt.size() + s->generated.size() >= s->max_total) s->finished = true;
+    };
     for (uint32_t i = 0; i < S; i++) {
         Seq* s = e->slots[i];
-        if (!s || s->finished) continue;
-        bool is_new = false;
-        for (Seq* a : admitted) is_new |= (a == s);
-        if (s->prefilling) {
-            if (is_new || !join_now) { running++; continue; }  // still only a prompt in flight
-            s->prefilling = false;                               // joined: this step sampled its first token
-            is_new = true;
-        }
-        s->cached = is_new ? (uint32_t)s->prompt.size() : s->cached + 1;
-        now.fill.emplace_back(s, (uint32_t)s->generated.size());
-        now.fill_slot.push_back(i);
-        s->generated.push_back(0);
-        const uint32_t total = (uint32_t)(s->prompt.size() + s->generated.size());
-        if (total >= s->max_total) s->finished = true;
-        else running++;
+        if (!s || s->finished || s->in_prefill) continue;
+        s->cached++;
+        emit_token(s);
     }
-    if (join_now && !detach) e->pf_active = false;
+    for (const Work& wk : work) {
+        wk.s->prefilled += wk.n;
+        if (!wk.last) continue;
+        wk.s->in_prefill = false;
+        wk.s->cached = (uint32_t)wk.s->prompt.size();
+        emit_token(wk.s);
+    }
+    while (!e->prefill_queue.empty() && !e->prefill_queue.front()->in_prefill) e->prefill_queue.pop_front();
+    uint32_t running = 0;
+    for (uint32_t i = 0; i < S; i++) if (e->slots[i] && !e->slots[i]->finished) running++;
     // the previous step (other bank) has had this step's host work to finish in: read its tokens now
     rc = collect(e);
     if (rc) return rc;
@@ -353,7 +363,6 @@ int ak_engine_step(ak_engine* e, uint32_t* n_running, uint32_t* n_waiting) {
     e->stats.h2d_bytes = r.h2d_bytes;
     e->stats.launch_host_ms_total = r.launch_host_ms - e->launch_host_base;
     e->stats.d2h_bytes = r.d2h_bytes;
-    (void)mc;
     if (n_running) *n_running = running;
     if (n_waiting) *n_waiting = (uint32_t)e->waiting.size();
     return AK_OK;
@@ -371,7 +380,7 @@ int ak_engine_run(ak_engine* e, uint64_t max_steps, uint64_t* steps_done) {
         n++;
         if (running == 0 && waiting == 0) break;
         // nothing runs, nothing was launched, yet sequences wait: no later step can admit them either
-        AK_REQUIRE(!(running == 0 && e->stats.steps == launched0 && !e->pf_active), AK_ERR_INVALID_ARG,
+        AK_REQUIRE(!(running == 0 && e->stats.steps == launched0), AK_ERR_INVALID_ARG,
                    "ak_engine_run: %u waiting sequence(s) can never be admitted (KV pool or step budget too small)", waiting);
     }
     int rc = collect(e);

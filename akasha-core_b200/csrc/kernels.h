@@ -100,17 +100,19 @@ int tp_all_reduce_f32(ak_ctx* ctx, float* buf, size_t count);
 // ---- attn_prefill.cu ---------------------------------------------------------------------------
 // Causal varlen attention over newly prefilled sequences. q/out rows of sequence i are
 // [cu[i], cu[i+1]) (+ row_base); K/V are read from the paged pools through the sequence's
-// block table (block_tables[seq_slot[i]]). Query row j of a sequence sits at position j.
+// block table (block_tables[seq_slot[i]]). Query row j of a sequence sits at position pos0[i] + j and attends to
+// positions 0 .. pos0[i] + j (pos0 == nullptr: all zero, a whole prompt; > 0: a later chunk of a prompt whose earlier
+// positions are already cached). pos0 is honoured by the tensor-core kernel only (bf16, head_dim 64 / 128).
 int launch_attn_prefill_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                               const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
-                              const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len,
+                              const int32_t* seq_slot, const int32_t* pos0, void* out, uint32_t n_seqs, uint32_t max_len,
                               uint32_t row_base, uint32_t heads, uint32_t head_dim, uint32_t block_size,
                               float scale, uint32_t dtype, uint64_t q_rows, uint64_t pool_blocks);
 // ---- attn_prefill_tc.cu: the same contract on the tensor cores (bf16, head_dim 64/128). q has
 // q_rows rows of heads*head_dim; the pools hold pool_blocks blocks. Waits that expire set a status word.
 int launch_attn_prefill_tc(cudaStream_t st, const void* q, uint64_t q_rows, const void* k_pool, const void* v_pool,
                            uint64_t pool_blocks, const int32_t* block_tables, uint32_t max_blocks_per_seq, const int32_t* cu,
-                           const int32_t* seq_slot, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base, uint32_t heads,
+                           const int32_t* seq_slot, const int32_t* pos0, void* out, uint32_t n_seqs, uint32_t max_len, uint32_t row_base, uint32_t heads,
                            uint32_t head_dim, float scale);
 int prefill_tc_status(unsigned int* out);
 // The reference emitter's contiguous form (f32 q/k/v [*,dim], optional l_cache).

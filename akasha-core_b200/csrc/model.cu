@@ -229,11 +229,8 @@ Runner::~Runner() {
     if (!ctx_) return;
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
-    if (st2_) cudaStreamSynchronize(st2_);  // a detached prefill may still be running
+    if (st2_) cudaStreamSynchronize(st2_);
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
-    if (ev_desc_) cudaEventDestroy(ev_desc_);
-    if (ev_pf_done_) cudaEventDestroy(ev_pf_done_);
-    for (auto& kv : pf_graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     if (ev_fork_) cudaEventDestroy(ev_fork_);
     if (ev_join_) cudaEventDestroy(ev_join_);
     if (st2_) cudaStreamDestroy(st2_);
@@ -279,7 +276,8 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     d_.out_rows = d_.kv_lens + max_seqs;
     d_.pf_cu = d_.out_rows + max_seqs;
     d_.pf_slot = d_.pf_cu + max_seqs + 1;
-    d_.block_tables = d_.pf_slot + max_seqs;
+    d_.pf_pos0 = d_.pf_slot + max_seqs;
+    d_.block_tables = d_.pf_pos0 + max_seqs;
     d_.rows = align_up(d_.block_tables + max_seqs * max_blocks_, 4);
     d_.total = d_.rows + max_rows_ * 4;
     for (Bank& b : banks_) {
@@ -359,8 +357,6 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaStreamCreateWithFlags(&st2_, cudaStreamNonBlocking));
     AK_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
     AK_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
-    AK_CUDA(cudaEventCreateWithFlags(&ev_desc_, cudaEventDisableTiming));
-    AK_CUDA(cudaEventCreateWithFlags(&ev_pf_done_, cudaEventDisableTiming));
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -376,8 +372,13 @@ int Runner::gemm(const void* a, const void* wt, void* c, uint32_t m, uint32_t n,
     return launch_gemm_bf16(st, a, wt, c, m, n, k, epi, n, true);
 }
 
+bool Runner::chunked_prefill_supported() const {
+    const uint32_t hd = w_->cfg.dim / w_->cfg.num_heads;
+    return w_->dtype == AK_BF16 && (hd == 64 || hd == 128) && tp_ == 1;
+}
+
 int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode,
-                          uint32_t n_splits, bool capturing, bool prompt_rows_only) {
+                          uint32_t n_splits, bool capturing) {
     cudaStream_t st = ctx_->stream;
     const ak_model_config& c = w_->cfg;
     // With tensor parallelism (tp_ > 1) this rank holds heads_l_ heads (dq_ = heads_l_*hd columns of
@@ -422,11 +423,22 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                 // Decode rows get their head split, RoPE and cache append inside the attention kernel (head sizes the
                 // TMA kernel handles); the separate kernel then only serves the prompt rows of the range.
                 const bool fuse = dec && attn_decode_fused_supported(hd);
+                // decode rows and a prompt chunk in one range: the chunk's attention (a dozen CTAs walking the chunk's
+                // keys one tile after the other) runs on the second stream BESIDE the decode attention, not after it
+                const bool side_pf = dec && pf && n_pf_seqs && s == st && two_streams_;
                 uint32_t a0 = r0, an = nr;
                 if (fuse) { a0 = max_seqs_; an = (r0 + nr > max_seqs_) ? r0 + nr - max_seqs_ : 0; }
                 if (an)
                     RC(launch_rope_kv_append(s, qkv_ + (size_t)a0 * 3 * Dq, rows + (size_t)a0 * 4 + 1, rows + (size_t)a0 * 4 + 2, 4,
                                              (char*)qbuf_ + (size_t)a0 * Dq * act, k_pool_[l], v_pool_[l], rope_table_, rope_len_, an, H, hd, 16, dt));
+                if (side_pf) {
+                    AK_CUDA(cudaEventRecord(ev_fork_, s));
+                    AK_CUDA(cudaStreamWaitEvent(st2_, ev_fork_, 0));
+                    RC(launch_attn_prefill_paged(st2_, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
+                                                 d_desc_ + d_.pf_slot, d_desc_ + d_.pf_pos0, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale,
+                                                 dt, max_rows_, n_blocks_));
+                    AK_CUDA(cudaEventRecord(ev_join_, st2_));
+                }
                 if (dec) {  // rows [0, max_seqs_): this range starts at row 0
                     ak_attn_decode_params p{};
                     p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
@@ -453,9 +465,12 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                         ev_valid_ = true;
                     }
                 }
-                if (pf && n_pf_seqs) {  // prompt rows are addressed from row max_seqs_ of the full buffers
+                if (side_pf) {
+                    AK_CUDA(cudaStreamWaitEvent(s, ev_join_, 0));
+                } else if (pf && n_pf_seqs) {  // prompt rows are addressed from row max_seqs_ of the full buffers
                     RC(launch_attn_prefill_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
-                                                 d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
+                                                 d_desc_ + d_.pf_slot, d_desc_ + d_.pf_pos0, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale,
+                                                 dt, max_rows_, n_blocks_));
                 }
                 RC(gemm_s(s, at, b.out, hid, nr, D, Dq, 1));
                 RC(launch_rmsnorm(s, hid, b.norm_2, xn, dt, nullptr, nr, D, c.norm_eps));
@@ -464,10 +479,10 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
             }
             return AK_OK;
         };
-        if (prompt_rows_only) {  // a detached prefill: the prompt rows alone, on the second stream, no sampling here
-            return range(st2_, max_seqs_, T - max_seqs_, false, true);
-        }
-        if (two_streams_ && any_decode && T > max_seqs_ && n_pf_seqs) {
+        // A step of at most 128 rows (the decode rows plus one prompt chunk) is ONE row tile of every projection: the
+        // prompt rows ride in the decode launches for free. Larger admission steps run the two kinds of rows as two
+        // ranges on two streams.
+        if (two_streams_ && any_decode && T > max_seqs_ && n_pf_seqs && T > 128) {
             AK_CUDA(cudaEventRecord(ev_fork_, st));
             AK_CUDA(cudaStreamWaitEvent(st2_, ev_fork_, 0));
             rc = range(st, 0, max_seqs_, true, false);
@@ -510,7 +525,8 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
             }
             if (n_pf_seqs) {
                 RC(launch_attn_prefill_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, max_blocks_, d_desc_ + d_.pf_cu,
-                                             d_desc_ + d_.pf_slot, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt, max_rows_, n_blocks_));
+                                             d_desc_ + d_.pf_slot, d_desc_ + d_.pf_pos0, attn_, n_pf_seqs, max_pf_len, max_seqs_, H, hd, 16, scale, dt,
+                                             max_rows_, n_blocks_));
             }
             if (tp) {
                 RC(gemm(attn_, b.out, tp_tmp_, T, D, Dq, 0));
@@ -594,12 +610,8 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
         for (uint32_t r = max_seqs_ + n_prefill_rows; r < max_seqs_ + rows_b; r++) rows[r] = {INT32_MIN, -1, -1, 0};
         int32_t* cu = h_pf_cu();
         int32_t* pfs = h_pf_slot();
-        for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; }
-    }
-    if (pf_inflight_ && n_prefill_rows == 0) {
-        // a detached prefill is reading the descriptor header on the device: this step's upload must carry the same values
-        memcpy(h_pf_cu(), pf_cu_saved_.data(), pf_cu_saved_.size() * sizeof(int32_t));
-        memcpy(h_pf_slot(), pf_slot_saved_.data(), pf_slot_saved_.size() * sizeof(int32_t));
+        int32_t* p0 = h_pf_pos0();
+        for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; p0[i] = 0; }
     }
     const uint64_t key = ((uint64_t)bank_ << 63) | ((uint64_t)rows_b << 32) | seqs_b;  // a graph bakes its bank's host buffers and events
     const uint32_t T = max_seqs_ + rows_b;
@@ -669,70 +681,6 @@ int Runner::mark_done() {
 int Runner::wait_bank(uint32_t b) {
     trace_dump();
     AK_CUDA(cudaEventSynchronize(banks_[b & 1u].ev_done));
-    return AK_OK;
-}
-
-int Runner::launch_prefill_detached(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len) {
-    AK_REQUIRE(n_prefill_rows >= 1 && n_prefill_rows <= max_pf_tokens_ && n_pf_seqs >= 1 && n_pf_seqs <= max_seqs_, AK_ERR_INVALID_ARG,
-               "runner: detached prefill exceeds its budget");
-    AK_REQUIRE(!pf_inflight_ && tp_ == 1, AK_ERR_INVALID_ARG, "runner: one detached prefill at a time, single GPU only");
-    AK_CUDA(cudaSetDevice(ctx_->device));
-    cudaStream_t st = ctx_->stream;
-    (void)max_pf_len;
-    uint32_t rows_b = pow2_bucket(n_prefill_rows, 64);
-    if (rows_b > max_pf_tokens_) rows_b = max_pf_tokens_;
-    uint32_t seqs_b = pow2_bucket(n_pf_seqs, 1);
-    if (seqs_b > max_seqs_) seqs_b = max_seqs_;
-    const uint32_t len_b = rows_b < max_seq_len_ ? rows_b : max_seq_len_;
-    RowInfo* rows = h_rows();
-    for (uint32_t r = max_seqs_ + n_prefill_rows; r < max_seqs_ + rows_b; r++) rows[r] = {INT32_MIN, -1, -1, 0};
-    int32_t* cu = h_pf_cu();
-    int32_t* pfs = h_pf_slot();
-    for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; }
-    // the decode-only steps that run beside this prefill re-upload the descriptor header: keep ours in it
-    pf_cu_saved_.assign(cu, cu + seqs_b + 1);
-    pf_slot_saved_.assign(pfs, pfs + seqs_b);
-    const uint32_t T = max_seqs_ + rows_b;
-    const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
-    const uint32_t n_splits = attn_decode_pick_splits(max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, max_seq_len_);
-    // main stream: the whole descriptor (header + decode rows + prompt rows); the prompt graph starts after it
-    AK_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st));
-    h2d_bytes += bytes;
-    AK_CUDA(cudaEventRecord(ev_desc_, st));
-    AK_CUDA(cudaStreamWaitEvent(st2_, ev_desc_, 0));
-    const uint64_t key = ((uint64_t)rows_b << 32) | seqs_b;
-    auto it = pf_graphs_.find(key);
-    if (it == pf_graphs_.end()) {
-        // first use of this shape: an eager pass (it IS this prefill), then the capture for the next time
-        int rc = launch_layers(T, rows_b, seqs_b, len_b, false, n_splits, false, true);
-        if (rc) return rc;
-        AK_CUDA(cudaStreamSynchronize(st2_));
-        cudaGraph_t graph = nullptr;
-        AK_CUDA(cudaStreamBeginCapture(st2_, cudaStreamCaptureModeThreadLocal));
-        const unsigned long long l0 = g_launch_count;
-        rc = launch_layers(T, rows_b, seqs_b, len_b, false, n_splits, true, true);
-        StepGraph g;
-        g.kernels = g_launch_count - l0;
-        g_launch_count = l0;
-        cudaError_t e2 = cudaStreamEndCapture(st2_, &graph);
-        if (rc) return rc;
-        if (e2 != cudaSuccess) return cuda_fail(e2, "cudaStreamEndCapture", __FILE__, __LINE__);
-        AK_CUDA(cudaGraphInstantiate(&g.exec, graph, 0));
-        cudaGraphDestroy(graph);
-        pf_graphs_[key] = g;
-    } else {
-        AK_CUDA(cudaGraphLaunch(it->second.exec, st2_));
-        g_launch_count += it->second.kernels;
-    }
-    AK_CUDA(cudaEventRecord(ev_pf_done_, st2_));
-    pf_inflight_ = true;
-    return AK_OK;
-}
-
-int Runner::join_prefill() {
-    if (!pf_inflight_) return AK_OK;
-    AK_CUDA(cudaStreamWaitEvent(ctx_->stream, ev_pf_done_, 0));
-    pf_inflight_ = false;
     return AK_OK;
 }
 

@@ -63,7 +63,7 @@ struct RowInfo {
 };
 
 struct StepDesc {  // offsets (in int32 units) into the descriptor buffer
-    uint32_t kv_lens, out_rows, pf_cu, pf_slot, block_tables, rows, total;
+    uint32_t kv_lens, out_rows, pf_cu, pf_slot, pf_pos0, block_tables, rows, total;
 };
 
 class Runner {
@@ -76,6 +76,11 @@ class Runner {
     int32_t* h_out_rows() { return h_desc_ + d_.out_rows; }
     int32_t* h_pf_cu() { return h_desc_ + d_.pf_cu; }
     int32_t* h_pf_slot() { return h_desc_ + d_.pf_slot; }
+    // position of the first prompt row of every prefilled sequence of the step: 0 for a whole prompt, the number of
+    // tokens already cached when the prompt is prefilled in chunks over several steps
+    int32_t* h_pf_pos0() { return h_desc_ + d_.pf_pos0; }
+    // chunked prefill needs the tensor-core prefill kernel, which takes the chunk's first position (bf16, head_dim 64/128)
+    bool chunked_prefill_supported() const;
     int32_t* h_block_table(uint32_t seq) { return h_desc_ + d_.block_tables + (size_t)seq * max_blocks_; }
     RowInfo* h_rows() { return reinterpret_cast<RowInfo*>(h_desc_ + d_.rows); }
     const uint32_t* h_sampled() const { return h_sampled_; }
@@ -88,13 +93,6 @@ class Runner {
     // Any step (decode rows + optional prefill rows) through a per-bucket captured graph.
     int run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len);
     int sync();
-    // Detached prefill: the admitted prompts' rows (described in the current bank, as for run_graph) run on
-    // the second stream as a graph of their own and are NOT joined to this step; following decode-only steps
-    // run beside them. join_prefill() makes the main stream wait for them (device side); the step launched
-    // after it may read the prompts' last hidden rows through out_rows. One detached prefill at a time.
-    int launch_prefill_detached(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len);
-    int join_prefill();
-    bool prefill_in_flight() const { return pf_inflight_; }
     // Two banks of host-side step state (pinned descriptor, pinned result buffer, timing events, captured
     // graphs), so that the host can describe and launch step N+1 while step N is still running. The
     // accessors above and run()/run_graph() use the current bank; the device buffers are shared and
@@ -125,8 +123,7 @@ class Runner {
     uint64_t graph_kernels = 0;              // kernel launches recorded in the captured decode step
 
    private:
-    int launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t n_splits, bool capturing,
-                      bool prompt_rows_only = false);
+    int launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, uint32_t max_pf_len, bool any_decode, uint32_t n_splits, bool capturing);
     int gemm(const void* a, const void* w, void* c, uint32_t m, uint32_t n, uint32_t k, int mode);
 
     ak_ctx* ctx_ = nullptr;
@@ -188,11 +185,6 @@ class Runner {
     cudaStream_t st2_ = nullptr;
     cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
     bool two_streams_ = true;
-    // detached prefill state
-    std::map<uint64_t, StepGraph> pf_graphs_;   // key = (prefill row bucket << 32) | prefill sequence bucket
-    cudaEvent_t ev_desc_ = nullptr, ev_pf_done_ = nullptr;
-    bool pf_inflight_ = false;
-    std::vector<int32_t> pf_cu_saved_, pf_slot_saved_;   // descriptor header of the prefill in flight
 };
 
 }  // namespace ak

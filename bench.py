@@ -180,8 +180,8 @@ def main():
     ap.add_argument("--cpu-config1", action="store_true", help="print the reference CPU configuration's numbers and exit")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--sync-steps", action="store_true", help="read every step's tokens before launching the next one")
-    ap.add_argument("--detached-prefill", action="store_true",
-                    help="prefill an admitted prompt beside the following decode steps instead of inside its admission step")
+    ap.add_argument("--chunked-prefill", action="store_true",
+                    help="prefill a prompt admitted while others decode in 64-row chunks that ride in the decode launches")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -220,7 +220,7 @@ def main():
     w.init_synthetic(seed=0, std=0.02)  # N(0, 0.02) matrices, N(1, 0.02) gains, generated on the device
     eng = ak.Engine(ctx, w, max_seqs=MAX_SEQS, max_seq_len=TOTAL_LEN, use_cuda_graph=not args.no_graph,
                     stop_on_eos=False, attn_timing=True, async_steps=not args.sync_steps,
-                    detached_prefill=args.detached_prefill)
+                    prefill_chunk_rows=128 - MAX_SEQS if args.chunked_prefill else 0)
     prompts = make_prompts(ak, rank)
     gen_per_job = sum(TOTAL_LEN - len(p) for p in prompts)
     ext = torch.cuda.ExternalStream(ctx.stream, device=local_rank)
@@ -336,7 +336,7 @@ def main():
                        "graph_launches": st["graph_launches"], "eager_steps": st["eager_steps"],
                        "host_counted_launches": int(eager_launches), "engine_steps_per_job": steps_per_job,
                        "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps,
-                       "detached_prefill": args.detached_prefill,
+                       "chunked_prefill": args.chunked_prefill,
                        # rank 0, per job (one pass over the 256 sequences): where the time goes
                        "gpu_ms_per_job": st["step_gpu_ms_total"] / args.steps,
                        "launch_host_ms_per_job": st["launch_host_ms_total"] / args.steps,

@@ -369,11 +369,14 @@ typedef struct ak_engine_config {
                                 * Needs stop_on_eos == 0 (sequence ends must be known without the tokens);
                                 * ignored otherwise. poll / block_table / get_stats / clear_finished / run wait for
                                 * the step in flight first. */
-    uint32_t detached_prefill; /* 1: a prompt admitted while other sequences are decoding is prefilled on a second stream,
-                                * beside the following decode-only steps, and joins the batch two steps later (its first
-                                * token is sampled in that step). No other admission until it has joined. Tokens per
-                                * sequence are unchanged; admission times, hence block tables, can differ from the
-                                * default engine. Needs use_cuda_graph; ignored with tensor parallelism. */
+    uint32_t prefill_chunk_rows; /* Chunked prefill. 0 (default): every admitted prompt is prefilled whole, in the step that
+                                  * admits it. N > 0: while other sequences are decoding, an admitted prompt is prefilled N rows
+                                  * per step and its sequence samples its first token in the step that holds its last chunk; with
+                                  * max_seqs + N <= 128 decode rows and prompt rows share ONE 128-row tile of every projection and
+                                  * the prompt rides in the decode launches (no step is stretched by a long prompt). Needs bf16
+                                  * weights, head_dim 64 or 128, no tensor parallelism; ignored otherwise. Tokens per sequence are
+                                  * the same either way; admission times, hence block tables, differ. With nobody decoding, or more
+                                  * than 8 chunks of prompt pending, prompts are prefilled whole. */
 } ak_engine_config;
 
 AK_API int ak_engine_create(ak_ctx* ctx, ak_weights* w, const ak_engine_config* cfg, ak_engine** out);

@@ -66,7 +66,7 @@ pub struct AkEngineConfig {
     pub stop_on_eos: u32,
     pub attn_timing: u32,
     pub async_steps: u32,
-    pub detached_prefill: u32,
+    pub prefill_chunk_rows: u32,
 }
 
 #[repr(C)]

@@ -11,7 +11,9 @@ Checked here, at that size:
       admitted later into a freed slot while 63 others decode (an admission step);
   (b) the asynchronous engine (the benchmark's mode) produces the same ids and block tables as
       the synchronous one;
-  (c) agreement with the CPU oracle in its bf16-emulating mode, teacher-forced with the GPU's
+  (c) chunked prefill (prompts prefilled 64 rows per step inside the decode launches) produces the
+      same ids as whole-prompt prefill;
+  (d) agreement with the CPU oracle in its bf16-emulating mode, teacher-forced with the GPU's
       tokens, reported as a match rate (bit-exact ids are only claimed in fp32 parity mode:
       src/nn/inference.rs:264-326 defines per-sequence greedy generation, and a bf16 tensor-core
       sum rounds differently from the oracle's scalar loops where two logits are nearly tied).
@@ -38,9 +40,9 @@ def workload(ak):
     return [ak.uniform_tokens(int(l), 50257, seed=10_000 + i) for i, l in enumerate(lens)]
 
 
-def run(ak, ctx, w, prompts, async_steps):
+def run(ak, ctx, w, prompts, async_steps, prefill_chunk_rows=0):
     e = ak.Engine(ctx, w, max_seqs=MAX_SEQS, max_seq_len=TOTAL_LEN, use_cuda_graph=True, stop_on_eos=False,
-                  async_steps=async_steps)
+                  async_steps=async_steps, prefill_chunk_rows=prefill_chunk_rows)
     ids = [e.submit(p, TOTAL_LEN) for p in prompts]
     steps = e.run_to_completion()
     outs, tables = [], []
@@ -93,6 +95,19 @@ def test_cfg3_async_equals_sync(ak, ctx, model, full_run):
         assert a.tolist() == b.tolist()
     for a, b in zip(tables, s_tables):
         assert a.tolist() == b.tolist()
+
+
+def test_cfg3_chunked_prefill_same_tokens(ak, ctx, model, full_run):
+    """Chunked prefill at the benchmark's size: prompts admitted while others decode are prefilled 64 rows per
+    step inside the decode launches (64 + 64 rows = one 128-row tile of every projection, the chunk's attention
+    through the tensor-core prefill kernel with a position offset). Every one of the 256 sequences generates
+    exactly the ids of the whole-prompt run."""
+    _, _, w = model
+    prompts, outs, _, steps = full_run
+    c_outs, _, c_steps = run(ak, ctx, w, prompts, async_steps=True, prefill_chunk_rows=128 - MAX_SEQS)
+    assert c_steps >= steps
+    for i, (a, b) in enumerate(zip(outs, c_outs)):
+        assert a.tolist() == b.tolist(), f"sequence {i}: ids differ between whole-prompt and chunked prefill"
 
 
 def test_cfg3_bf16_oracle_match_rate(ak, orc, model, full_run):

@@ -194,9 +194,9 @@ def test_akasha_hall_config1_parity(ak, orc, ctx):
 
 
 # ================================================================================ engine
-def run_engine(ak, ctx, w, prompts, total_len, max_seqs, graph, max_seq_len=None, async_steps=False, detached_prefill=False):
+def run_engine(ak, ctx, w, prompts, total_len, max_seqs, graph, max_seq_len=None, async_steps=False, prefill_chunk_rows=0):
     e = ak.Engine(ctx, w, max_seqs=max_seqs, max_seq_len=max_seq_len or total_len, use_cuda_graph=graph,
-                  async_steps=async_steps, detached_prefill=detached_prefill)
+                  async_steps=async_steps, prefill_chunk_rows=prefill_chunk_rows)
     ids = [e.submit(p, total_len) for p in prompts]
     steps = e.run_to_completion(100000)
     outs, tables = [], []
@@ -309,24 +309,26 @@ def test_engine_async_steps_equal_sync_steps(ak, ctx, dtype_name):
     e.close(); w.close()
 
 
-@pytest.mark.parametrize("dtype_name,async_steps", [("f32", False), ("bf16", True)])
-def test_engine_detached_prefill_same_tokens(ak, ctx, dtype_name, async_steps):
-    """A prompt admitted while others decode is prefilled on the second stream beside the next decode
-    steps and joins two steps later: every sequence still generates exactly the tokens it generates
-    in the default engine (more sequences than slots, so most admissions take the detached path; with
-    2 slots the batch also runs empty while a prompt is in flight)."""
-    cfg = ak.ModelConfig(600, 128, 2, 2, 96)
-    dt = ak.AK_F32 if dtype_name == "f32" else ak.AK_BF16
-    _, w = make(ak, ctx, cfg, 0, 0.06, dt)
-    total, n = 96, 13
-    lens = ak.uniform_ints(n, 3, 70, seed=9)
+@pytest.mark.parametrize("async_steps", [False, True])
+def test_engine_chunked_prefill_same_tokens(ak, ctx, async_steps):
+    """bf16, head_dim 64: a prompt admitted while others decode is prefilled in chunks that ride in the decode
+    launches (one 128-row tile: decode rows + chunk) and its sequence samples its first token with its last chunk.
+    Every sequence still generates exactly the tokens it generates when its prompt is prefilled whole: chunk
+    boundaries only move query rows between launches, a row's arithmetic does not depend on its launch-mates.
+    More sequences than slots, so most admissions happen while others decode; with 2 slots the batch also runs
+    empty while a prompt is pending (the rest of it is then prefilled whole, from its current position)."""
+    cfg = ak.ModelConfig(600, 128, 2, 2, 200)
+    _, w = make(ak, ctx, cfg, 0, 0.06, ak.AK_BF16)
+    total, n = 200, 13
+    lens = ak.uniform_ints(n, 3, 170, seed=9)
     prompts = [ak.uniform_tokens(int(l), cfg.vocab_size, seed=500 + i) for i, l in enumerate(lens)]
-    for max_seqs in (4, 2):
-        ref, _, rst, _ = run_engine(ak, ctx, w, prompts, total, max_seqs, True)
-        got, _, gst, _ = run_engine(ak, ctx, w, prompts, total, max_seqs, True, async_steps=async_steps, detached_prefill=True)
-        for a, b in zip(got, ref):
-            assert a.tolist() == b.tolist()
+    for max_seqs, chunk in ((4, 124), (2, 126), (4, 16), (4, 100)):
+        ref, _, rst, rsteps = run_engine(ak, ctx, w, prompts, total, max_seqs, True, prefill_chunk_rows=0)
+        got, _, gst, gsteps = run_engine(ak, ctx, w, prompts, total, max_seqs, True, async_steps=async_steps, prefill_chunk_rows=chunk)
+        for i, (a, b) in enumerate(zip(got, ref)):
+            assert a.tolist() == b.tolist(), f"max_seqs {max_seqs}, chunk {chunk}: sequence {i} differs"
         assert gst["prefill_tokens"] == rst["prefill_tokens"] and gst["decode_tokens"] == rst["decode_tokens"]
+        assert gsteps >= rsteps     # chunks spread an admission over several steps
     w.close()
 
 
