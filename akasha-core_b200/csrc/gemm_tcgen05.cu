@@ -718,6 +718,15 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
         if (sk.ks > 1) {
             const uint32_t mt = cdiv(m, GB_M);
+#ifdef AK_MIDM_KSEG2_BN
+            if (mt <= 4 && sk.ks == 2) {   // experiment: two in-CTA K segments instead of a 2-CTA cluster exchange
+                p.kseg = 2; p.ks = 1; p.bn = AK_MIDM_KSEG2_BN;
+                uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
+                if (st > G_MAX_STAGES) st = G_MAX_STAGES;
+                p.stages = st < num_kb ? st : num_kb;
+                return p;
+            }
+#endif
             if (mt <= 4) {
                 // A prompt or two joining a decode batch: the K chain per CTA, not the flop count, sets the
                 // time (one MMA costs ~150 cycles whatever its width), so keep the cluster split of the

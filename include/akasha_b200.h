@@ -58,6 +58,10 @@ AK_API const char* ak_last_error_string(void);
 AK_API const char* ak_version(void);
 /* Kernel launches issued by this library on the calling thread since it loaded. */
 AK_API unsigned long long ak_launch_count(void);
+/* Environment switches read by the library (both are measurement aids, off by default):
+ *   AK_PDL=0    launch every kernel without the programmatic-dependent-launch attribute (A/B timing of the overlap);
+ *   AK_TRACE=1  record an event after every launch of a step and print per-kernel in-stream times to stderr
+ *               (the events remove the overlap between kernels, so the figures are upper bounds). */
 /* Synchronise `stream` and read the device status words: AK_ERR_DEVICE_WAIT if a bounded
  * device-side wait (mbarrier / TMA / tcgen05 pipeline) ever ran out, AK_OK otherwise. */
 AK_API int ak_check_device_status(void* stream);

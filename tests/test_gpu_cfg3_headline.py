@@ -64,16 +64,31 @@ def full_run(ak, ctx, model):
     return prompts, outs, tables, steps
 
 
-def test_cfg3_token_counts_and_block_tables(ak, full_run):
+def test_cfg3_token_counts_and_block_tables(ak, orc, full_run):
     prompts, outs, tables, steps = full_run
     assert sum(len(o) for o in outs) == sum(TOTAL_LEN - len(p) for p in prompts)
     for p, o, t in zip(prompts, outs, tables):
         assert len(o) == TOTAL_LEN - len(p)
         assert len(t) == TOTAL_LEN // 16 and len(set(t.tolist())) == len(t)
         assert o.max() < 50257
-    # the first 64 sequences are admitted together and take blocks lowest-index-first, in order
-    for i in range(MAX_SEQS):
-        assert tables[i].tolist() == list(range(32 * i, 32 * i + 32))
+    # KV slot indexing is exact: replay the scheduler's admission / retire order on the oracle's allocator (lowest
+    # free block first, 32 blocks reserved per sequence, a finished sequence's blocks returned before the next
+    # admission) and compare every one of the 256 block tables
+    pool = orc.BlockPool(MAX_SEQS * (TOTAL_LEN // 16))
+    need, n = TOTAL_LEN // 16, len(prompts)
+    live, waiting, expect, step = {}, list(range(n)), {}, 0
+    while waiting or live:
+        for i in [i for i, f in live.items() if f <= step]:
+            for b in expect[i]:
+                pool.free(int(b))
+            del live[i]
+        while waiting and len(live) < MAX_SEQS:
+            i = waiting.pop(0)
+            expect[i] = [pool.alloc() for _ in range(need)]
+            live[i] = step + (TOTAL_LEN - len(prompts[i]))   # one token per step, the first one in the admission step
+        step += 1
+    for i in range(n):
+        assert tables[i].tolist() == expect[i], f"sequence {i}: block table differs from the allocator replay"
 
 
 def test_cfg3_batch_invariance(ak, ctx, model, full_run):
