@@ -34,6 +34,9 @@
 #include "kernels.h"
 #include "tma.h"
 
+#include <algorithm>
+#include <vector>
+
 namespace ak {
 
 __device__ unsigned int g_attn_decode_status = 0;
@@ -104,6 +107,9 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 // Fused split + RoPE + append (see the top of the file). qkv == nullptr: plain attention over q.
 struct DecFused {
+    // Optional launch order of the rows: CTA (h, y) works on row row_order[y]. A permutation only moves work between
+    // CTAs (hence between SMs); the engine uses it to give every SM a similar number of KV bytes.
+    const int32_t* row_order;
     const float* qkv;       // [rows, 3 * heads * HD] f32: q | k | v of the step's new token of every sequence
     const float2* rope;     // [rope_len][HD / 2] (cos, sin)
     uint32_t rope_len;
@@ -208,7 +214,8 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     __shared__ float sm_m[DEC_WARPS], sm_l[DEC_WARPS];
     __shared__ float sm_acc[DEC_WARPS][HD];
 
-    const uint32_t h = blockIdx.x, row = blockIdx.y, split = blockIdx.z;
+    const uint32_t h = blockIdx.x, split = blockIdx.z;
+    const uint32_t row = fz.row_order ? (uint32_t)fz.row_order[blockIdx.y] : blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t* table = block_tables + (size_t)row * max_blocks;
     // Unsplit launches know their blocks' table entries without the length: fetch both at once (one memory
@@ -694,6 +701,32 @@ static int launch_decode(cudaStream_t st, const void* q, const void* k_pool, con
 
 bool attn_decode_fused_supported(uint32_t head_dim) { return head_dim == 64 || head_dim == 128; }
 
+// CTAs are handed to the SMs in launch order, one per SM and round: CTA number c = y * heads + h lands on SM c mod 148
+// as that SM's (c / 148)-th CTA. A launch that fits one wave therefore gives every SM one row out of each "level" of
+// 148 / heads consecutive y. Rows sorted by length are dealt to the levels in a snake (level 0 longest first, level 1
+// shortest first, ...), so every SM gets a long row with a short one and the last, partly filled level holds the
+// shortest rows. A launch of several waves gets the longest rows first (the short ones fill the tail).
+void attn_decode_row_order(const int32_t* kv_lens, uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, int32_t* order_out) {
+    std::vector<uint32_t> by_len(rows);
+    for (uint32_t i = 0; i < rows; i++) by_len[i] = i;
+    std::stable_sort(by_len.begin(), by_len.end(), [&](uint32_t a, uint32_t b) { return kv_lens[a] > kv_lens[b]; });
+    const bool one_wave = (uint64_t)rows * heads <= wave_slots(head_dim, kv_dtype, DEC_STAGES);
+    if (!one_wave || heads == 0) {
+        for (uint32_t i = 0; i < rows; i++) order_out[i] = (int32_t)by_len[i];
+        return;
+    }
+    // positions y in the order in which the sorted rows are dealt: by level, alternating direction
+    std::vector<uint32_t> pos(rows);
+    for (uint32_t y = 0; y < rows; y++) pos[y] = y;
+    auto level = [&](uint32_t y) { return (uint32_t)(((uint64_t)y * heads) / 148); };
+    std::stable_sort(pos.begin(), pos.end(), [&](uint32_t a, uint32_t b) {
+        const uint32_t la = level(a), lb = level(b);
+        if (la != lb) return la < lb;
+        return (la & 1u) ? a > b : a < b;
+    });
+    for (uint32_t i = 0; i < rows; i++) order_out[pos[i]] = (int32_t)by_len[i];
+}
+
 int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool, const void* v_pool,
                              const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
                              const ak_attn_decode_params& p, bool counters_are_zero) {
@@ -701,12 +734,12 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
 }
 
 int launch_attn_decode_fused(cudaStream_t st, const float* qkv, const float2* rope_table, uint32_t rope_len, void* k_pool, void* v_pool,
-                             const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                             const int32_t* block_tables, const int32_t* kv_lens, const int32_t* row_order, void* out, void* scratch,
                              const ak_attn_decode_params& p, bool counters_are_zero) {
     AK_REQUIRE(attn_decode_fused_supported(p.head_dim) && ((uintptr_t)k_pool % 16 == 0) && ((uintptr_t)v_pool % 16 == 0) && ((uintptr_t)qkv % 16 == 0),
                AK_ERR_UNSUPPORTED, "attn_decode_fused: head_dim must be 64 or 128 and the buffers 16-byte aligned");
     AK_REQUIRE(rope_table && rope_len, AK_ERR_INVALID_ARG, "attn_decode_fused: a RoPE table is required");
-    DecFused fz{qkv, rope_table, rope_len, k_pool, v_pool};
+    DecFused fz{row_order, qkv, rope_table, rope_len, k_pool, v_pool};
     return launch_decode(st, qkv, k_pool, v_pool, block_tables, kv_lens, out, scratch, p, counters_are_zero, fz);
 }
 
@@ -775,7 +808,7 @@ int ak_attn_decode_append_paged(void* stream, const float* qkv, const float* rop
     AK_REQUIRE(qkv && rope_table && k_pool && v_pool && block_tables && kv_lens && out, AK_ERR_INVALID_ARG, "ak_attn_decode_append_paged: null pointer");
     AK_REQUIRE(p.block_size == DEC_BS && p.kv_dtype <= AK_BF16, AK_ERR_INVALID_ARG, "ak_attn_decode_append_paged: block_size must be 16, kv_dtype f32 or bf16");
     return launch_attn_decode_fused(as_stream(stream), qkv, reinterpret_cast<const float2*>(rope_table), rope_len, k_pool, v_pool, block_tables,
-                                    kv_lens, out, scratch, p, false);
+                                    kv_lens, nullptr, out, scratch, p, false);
 }
 }
 

@@ -58,14 +58,26 @@ int launch_embed_rows(cudaStream_t st, const int32_t* tok_src, uint32_t idx_stri
 // ============================================================================ rmsnorm
 // src/shaders/cuda.rs:421-456: y = x * (1/sqrt(ss/size + eps)) * w. One warp per row, the row is
 // read once with 128-bit loads and held in registers when it fits (size <= 32*4*RCACHE).
-template <typename OT, bool HAS_RES, bool ROPE>
+template <typename OT, bool HAS_RES, bool ROPE, bool EARLY_W>
 __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ residual,
                                     const float* __restrict__ w, OT* __restrict__ y,
                                     const int32_t* __restrict__ row_map, const int32_t* __restrict__ positions,
                                     uint32_t rows, uint32_t size, float eps, uint32_t head_dim) {
+    constexpr int RCACHE = 8;  // float4 per lane kept in registers -> size <= 1024 cached
+    // EARLY_W (launches of a few rows inside a step's chain, where latency is everything): the norm weights do not
+    // depend on the preceding kernel, so they are fetched (a trip to HBM: each layer's are read once per step) before
+    // waiting for it. Launches of many rows keep the registers for occupancy instead.
+    const bool vec = (size & 3u) == 0;
+    float4 gcache[EARLY_W ? RCACHE : 1];
+    if (EARLY_W && vec) {
+#pragma unroll
+        for (int c = 0; c < RCACHE; c++) {
+            const uint32_t i = (threadIdx.x & 31) + 32u * c;
+            gcache[EARLY_W ? c : 0] = i < (size >> 2) ? reinterpret_cast<const float4*>(w)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     pdl_wait();
     pdl_trigger();
-    constexpr int RCACHE = 8;  // float4 per lane kept in registers -> size <= 1024 cached
     // RoPE frequencies 1 / 10000^(2i / head_dim): head_dim / 2 values for the whole launch, computed once per CTA
     __shared__ float s_freq[ROPE ? 128 : 1];
     const bool freq_tab = ROPE && head_dim <= 256;
@@ -84,7 +96,6 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
     }
     float* xr = x + (size_t)src_row * size;
     const float* rr = HAS_RES ? residual + (size_t)src_row * size : nullptr;
-    const bool vec = (size & 3u) == 0;
     float4 cache[RCACHE];
     float ss = 0.0f;
     if (vec) {
@@ -135,8 +146,7 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
     };
     if (same_d0) factors((lane * 4) % head_dim, hs0, hc0, hs1, hc1);
 
-    auto emit4 = [&](uint32_t i4, float4 v) {
-        float4 g = reinterpret_cast<const float4*>(w)[i4];
+    auto emit4 = [&](uint32_t i4, float4 v, float4 g) {
         float o0 = v.x * rs * g.x, o1 = v.y * rs * g.y, o2 = v.z * rs * g.z, o3 = v.w * rs * g.w;
         if (ROPE) {
             float s0 = hs0, c0 = hc0, s1 = hs1, c1 = hc1;
@@ -160,9 +170,9 @@ __global__ void rmsnorm_rows_kernel(float* __restrict__ x, const float* __restri
 #pragma unroll
         for (int c = 0; c < RCACHE; c++) {
             uint32_t i = lane + 32u * c;
-            if (i < nv) emit4(i, cache[c]);
+            if (i < nv) emit4(i, cache[c], EARLY_W ? gcache[EARLY_W ? c : 0] : reinterpret_cast<const float4*>(w)[i]);
         }
-        for (uint32_t i = lane + 32u * RCACHE; i < nv; i += 32) emit4(i, reinterpret_cast<const float4*>(xr)[i]);
+        for (uint32_t i = lane + 32u * RCACHE; i < nv; i += 32) emit4(i, reinterpret_cast<const float4*>(xr)[i], reinterpret_cast<const float4*>(w)[i]);
     } else {
         // scalar tail path (ROPE needs even sizes and is only offered on the vector path)
         for (uint32_t i = lane; i < size; i += 32) yr[i] = Cvt<OT>::from_f(xr[i] * rs * w[i]);
@@ -175,15 +185,15 @@ static int rmsnorm_dispatch(cudaStream_t st, float* x, const float* residual, co
                             float eps, uint32_t head_dim) {
     const int WARPS = 4;
     dim3 grid(cdiv(rows, WARPS)), block(WARPS * 32);
-    bool rope = head_dim != 0;
-    if (residual && rope)
-        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, true, true>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
-    else if (residual)
-        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, true, false>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
-    else if (rope)
-        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, false, true>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
-    else
-        AK_TRY(launch_k(rmsnorm_rows_kernel<OT, false, false>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, positions, rows, size, eps, head_dim));
+    const bool rope = head_dim != 0, early = rows <= 1024;
+#define AK_NORM_LAUNCH(RES, ROPE_, EARLY)                                                                                          \
+    AK_TRY(launch_k(rmsnorm_rows_kernel<OT, RES, ROPE_, EARLY>, dim3(grid), dim3(block), 0, st, NO_CLUSTER, x, residual, w, y, row_map, \
+                    positions, rows, size, eps, head_dim))
+    if (residual && rope) { if (early) AK_NORM_LAUNCH(true, true, true); else AK_NORM_LAUNCH(true, true, false); }
+    else if (residual) { if (early) AK_NORM_LAUNCH(true, false, true); else AK_NORM_LAUNCH(true, false, false); }
+    else if (rope) { if (early) AK_NORM_LAUNCH(false, true, true); else AK_NORM_LAUNCH(false, true, false); }
+    else { if (early) AK_NORM_LAUNCH(false, false, true); else AK_NORM_LAUNCH(false, false, false); }
+#undef AK_NORM_LAUNCH
     return AK_OK;
 }
 

@@ -80,7 +80,7 @@ __host__ __device__ constexpr uint32_t make_idesc(uint32_t m, uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-constexpr int G_MAX_STAGES = 8;
+constexpr int G_MAX_STAGES = 12;
 
 // Cluster-wide barrier for all threads of all CTAs of the cluster. The .aligned forms need every
 // thread of a warp to execute them together, and the producer / MMA lanes run ahead of their
@@ -99,11 +99,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 }
 
 template <int BN> struct GemmCfg {
-    static constexpr int A_BYTES = GB_M * GB_K * 2;   // 16 KB
-    static constexpr int B_BYTES = BN * GB_K * 2;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // multiple of 1024 for every BN % 8 == 0
-    static constexpr int TMEM_COLS = BN <= 32 ? 32 : (BN <= 64 ? 64 : (BN <= 128 ? 128 : 256));
-    static constexpr int RED_BYTES = GB_M * BN * 4;   // split-K exchange buffer [src][128][BN/ks]
+    static constexpr int B_BYTES = BN * GB_K * 2;   // weight tile of a stage; a multiple of 1024 for every BN % 8 == 0
 };
 
 // Epilogue arguments (by value).
@@ -270,7 +266,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t rank = SPLIT ? cluster.block_rank() : 0u;
 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    float* red = reinterpret_cast<float*>(smem + (size_t)stages * C::STAGE_BYTES);  // used when ks > 1
+    // A stage is [a_rows x 128 B of activations][BN x 128 B of weights]: a decode batch's slot is as small as its box,
+    // so the whole K range of a skinny CTA fits the ring and every weight tile is requested before the dependency
+    // wait. The MMA still reads 128 rows from the slot's base: what follows (the weights, the next slot, the tail
+    // padding behind the ring) feeds accumulator rows that are never stored.
+    const uint32_t a_bytes = a_rows * (GB_K * 2), stage_stride = a_bytes + C::B_BYTES;
+    float* red = reinterpret_cast<float*>(smem + (size_t)stages * stage_stride + (GB_M - a_rows) * (GB_K * 2));  // used when ks > 1
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t m0 = blockIdx.y * GB_M, n0 = blockIdx.x * BN;
     const uint32_t num_kb_total = (k + GB_K - 1) / GB_K;
@@ -310,24 +311,27 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             // requested BEFORE waiting for it, so the weight stream from HBM overlaps the
             // predecessor's tail. The activation tiles follow after the wait.
             const uint32_t pre = num_kb < stages ? num_kb : stages;
-            const uint32_t stage_tx = a_rows * (GB_K * 2) + C::B_BYTES;
+            const uint32_t stage_tx = stage_stride;
             for (uint32_t i = 0; i < pre; i++) {
-                uint8_t* b_dst = smem + (size_t)i * C::STAGE_BYTES + C::A_BYTES;
+                uint8_t* b_dst = smem + (size_t)i * stage_stride + a_bytes;
                 mbar_expect_tx(&full_bar[i], stage_tx);
                 tma_load_2d(b_dst, &tmB, (int32_t)((kb_begin + i) * GB_K), (int32_t)n0, &full_bar[i]);
             }
             pdl_wait();
             for (uint32_t i = 0; i < pre; i++)
-                tma_load_2d(smem + (size_t)i * C::STAGE_BYTES, &tmA, (int32_t)((kb_begin + i) * GB_K), (int32_t)m0, &full_bar[i]);
+                tma_load_2d(smem + (size_t)i * stage_stride, &tmA, (int32_t)((kb_begin + i) * GB_K), (int32_t)m0, &full_bar[i]);
+            // ring position and phase are carried, not derived from i: an integer division costs this one thread
+            // more than the four MMAs of a K block cost the tensor core
+            uint32_t s = 0, ph = 1;   // i == pre == stages here: slot 0, second use
             for (uint32_t i = pre; i < num_kb; i++) {
-                const uint32_t s = i % stages, ph = (i / stages) & 1u;
                 if (!mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); break; }
-                uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
-                uint8_t* b_dst = a_dst + C::A_BYTES;
+                uint8_t* a_dst = smem + (size_t)s * stage_stride;
+                uint8_t* b_dst = a_dst + a_bytes;
                 mbar_expect_tx(&full_bar[s], stage_tx);
                 const int32_t kx = (int32_t)((kb_begin + i) * GB_K);
                 tma_load_2d(a_dst, &tmA, kx, (int32_t)m0, &full_bar[s]);
                 tma_load_2d(b_dst, &tmB, kx, (int32_t)n0, &full_bar[s]);
+                if (++s == stages) { s = 0; ph ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -335,21 +339,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc(GB_M, BN);
             const uint32_t per_seg = (num_kb + kseg - 1) / kseg;
+            uint32_t s = 0, ph = 0, in_seg = 0, acc_col = tmem_base;   // carried (no division in the loop, see the producer)
             for (uint32_t i = 0; i < num_kb; i++) {
-                const uint32_t seg = i / per_seg, first_of_seg = (i - seg * per_seg) == 0;
-                const uint32_t s = i % stages, ph = (i / stages) & 1u;
                 if (!mbar_wait(&full_bar[s], ph)) { atomicExch(&fail_flag, 2u); break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
-                const uint32_t b_addr = a_addr + C::A_BYTES;
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * stage_stride);
+                const uint32_t b_addr = a_addr + a_bytes;
                 const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(b_addr);
 #pragma unroll
                 for (uint32_t kk = 0; kk < GB_K / 16; kk++) {
                     // advance 16 bf16 = 32 bytes along K inside the swizzle row: +2 in the address field
-                    tc_mma_f16(tmem_base + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                               (first_of_seg && kk == 0) ? 0u : 1u);
+                    tc_mma_f16(acc_col, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (in_seg == 0 && kk == 0) ? 0u : 1u);
                 }
-                tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it
+                if (num_kb > stages) tc_commit(&empty_bar[s]);  // stage reusable once these MMAs have read it (nobody waits when the ring holds the whole K range)
+                if (++s == stages) { s = 0; ph ^= 1u; }
+                if (++in_seg == per_seg) { in_seg = 0; acc_col += BN; }
             }
             if (num_kb > 0) tc_commit(&acc_bar);  // accumulator complete
             else mbar_arrive(&acc_bar);           // nothing to accumulate: this CTA contributes zeros
@@ -360,9 +364,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t quad = warp & 3u;
     const uint32_t trow = quad * 32 + lane;  // row inside the tile
     const uint32_t row = m0 + trow;
-    bool got = true;
+    bool got = true, pre_ok = false;
+    float4 pre0 = make_float4(0.f, 0.f, 0.f, 0.f), pre1 = pre0;
     if (warp >= 2) {
         pdl_wait();  // the epilogue reads and writes C: never before the preceding kernels are done
+        if (SPLIT && EPI == AK_EPI_ADD_F32) {
+            // the residual values this thread will add to: requested now, so that their L2 round trip runs under the
+            // main loop and the exchange instead of after them
+            const uint32_t SLp = (uint32_t)BN / ks, gc = n0 + rank * SLp;
+            pre_ok = row < m && SLp <= 8 && (ep.ldc & 3u) == 0 && gc + SLp <= n;
+            if (pre_ok) {
+                const float* src = reinterpret_cast<const float*>(ep.c) + (size_t)row * ep.ldc + gc;
+                pre0 = *reinterpret_cast<const float4*>(src);
+                if (SLp == 8) pre1 = *reinterpret_cast<const float4*>(src + 4);
+            }
+        }
         got = mbar_wait(&acc_bar, 0);
         if (!got && lane == 0) atomicExch(&fail_flag, 3u);
         got = __all_sync(0xffffffffu, got);  // warp-uniform: TMEM loads and the paired stores below are warp-collective
@@ -442,7 +458,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
                 }
                 float v[4] = {acc.x, acc.y, acc.z, acc.w};
-                epi_store<EPI, 4>(ep, row, n0 + rank * SL + j, v, n);
+                if (EPI == AK_EPI_ADD_F32 && pre_ok) {
+                    const float4 p = j == 0 ? pre0 : pre1;
+                    v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+                    epi_store<AK_EPI_STORE_F32, 4>(ep, row, n0 + rank * SL + j, v, n);
+                } else {
+                    epi_store<EPI, 4>(ep, row, n0 + rank * SL + j, v, n);
+                }
             }
         }
     }
@@ -573,13 +595,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         // ---------------- TMA producer (one per CTA; bytes are counted on the leader's full barriers)
         if (lane == 0) {
             pdl_wait();
-            uint32_t it = 0;
+            uint32_t it = 0, s = 0, ph = 0;   // ring position and phase are carried: no division in the K loop
             bool ok = true;
             for (uint32_t t = pair; t < tiles_total && ok; t += n_pairs) {
                 const uint32_t m0 = ((t / tiles_n) * 2 + rank) * GB_M;        // this CTA's 128 rows of the pair's 256
                 const uint32_t nb0 = (t % tiles_n) * BN + rank * (BN / 2);    // this CTA's half of the weight rows
                 for (uint32_t kb = 0; kb < num_kb; kb++, it++) {
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
                     if (it >= stages && !mbar_wait(&empty_bar[s], ph ^ 1u)) { atomicExch(&fail_flag, 1u); ok = false; break; }
                     uint8_t* a_dst = smem + (size_t)s * C::STAGE_BYTES;
                     const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
@@ -587,38 +608,48 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     const int32_t kx = (int32_t)(kb * GB_K);
                     tma_load_2d_pair(a_dst, &tmA, kx, (int32_t)m0, bar);
                     tma_load_2d_pair(a_dst + C::A_BYTES, &tmB, kx, (int32_t)nb0, bar);
+                    if (++s == stages) { s = 0; ph ^= 1u; }
                 }
             }
             // drain: every commit the leader addressed to this CTA's empty barriers has landed before the CTA may leave
-            for (uint32_t j = (it > stages ? it - stages : 0); j < it && ok; j++)
-                if (!mbar_wait(&empty_bar[j % stages], (j / stages) & 1u)) { atomicExch(&fail_flag, 5u); break; }
+            // (the last min(it, stages) uses, oldest first; with it >= stages the oldest one sits in slot s, the next to
+            // be overwritten, one round behind the carried phase)
+            if (ok && it > 0) {
+                const bool wrapped = it >= stages;
+                uint32_t ds = wrapped ? s : 0u, dph = wrapped ? (ph ^ 1u) : 0u;
+                const uint32_t cnt = wrapped ? stages : it;
+                for (uint32_t j = 0; j < cnt; j++) {
+                    if (!mbar_wait(&empty_bar[ds], dph)) { atomicExch(&fail_flag, 5u); break; }
+                    if (++ds == stages) { ds = 0; dph ^= 1u; }
+                }
+            }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer: one thread of the leader CTA drives both SMs' tensor cores
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = make_idesc(2 * GB_M, BN);
             const uint32_t per_seg = (num_kb + kseg - 1) / kseg;
-            uint32_t it = 0, tc = 0;
+            uint32_t tc = 0, s = 0, ph = 0;   // ring position and phase are carried: no division in the K loop
             bool ok = true;
             for (uint32_t t = pair; t < tiles_total && ok; t += n_pairs, tc++) {
                 const uint32_t buf = n_bufs == 2 ? (tc & 1u) : 0u, acc_ph = (n_bufs == 2 ? (tc >> 1) : tc) & 1u;
                 // the epilogue warps of both CTAs have drained this buffer (it was last used by tile tc - n_bufs)
                 if (tc >= n_bufs && !mbar_wait(&acc_empty[buf], acc_ph ^ 1u)) { atomicExch(&fail_flag, 4u); break; }
                 tc_fence_after();
-                for (uint32_t kb = 0; kb < num_kb; kb++, it++) {
-                    const uint32_t seg = kb / per_seg, first_of_seg = (kb - seg * per_seg) == 0;
-                    const uint32_t s = it % stages, ph = (it / stages) & 1u;
+                uint32_t in_seg = 0, acc_col = tmem_base + buf * buf_cols;
+                for (uint32_t kb = 0; kb < num_kb; kb++) {
                     if (!mbar_wait(&full_bar[s], ph)) { atomicExch(&fail_flag, 2u); ok = false; break; }
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * C::STAGE_BYTES);
                     const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + C::A_BYTES);
 #pragma unroll
                     for (uint32_t kk = 0; kk < GB_K / 16; kk++)
-                        tc_mma2_f16(tmem_base + buf * buf_cols + seg * BN, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc,
-                                    (first_of_seg && kk == 0) ? 0u : 1u);
+                        tc_mma2_f16(acc_col, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (in_seg == 0 && kk == 0) ? 0u : 1u);
                     // the stage is reusable in BOTH CTAs once these MMAs have read it
                     tc_commit2(map_to_cta(smem_u32(&empty_bar[s]), 0));
                     tc_commit2(map_to_cta(smem_u32(&empty_bar[s]), 1));
+                    if (++s == stages) { s = 0; ph ^= 1u; }
+                    if (++in_seg == per_seg) { in_seg = 0; acc_col += BN; }
                 }
                 if (!ok) break;
                 tc_commit2(map_to_cta(smem_u32(&acc_full[buf]), 0));
@@ -704,7 +735,11 @@ static uint32_t a_box_rows(uint32_t m) {
     if (m > 64) return GB_M;
     return m > 32 ? 64 : (m > 16 ? 32 : 16);
 }
-static uint32_t stage_bytes(uint32_t bn) { return GB_M * GB_K * 2 + bn * GB_K * 2; }
+static uint32_t stage_bytes(uint32_t bn, uint32_t a_rows = GB_M) { return a_rows * GB_K * 2 + bn * GB_K * 2; }
+// shared memory of the one-CTA kernel: the ring, the rows an MMA reads past a short activation slot, the exchange buffer
+static size_t gemm_smem_bytes(uint32_t stages, uint32_t bn, uint32_t a_rows, bool split) {
+    return (size_t)stages * stage_bytes(bn, a_rows) + (GB_M - a_rows) * GB_K * 2 + (split ? (size_t)GB_M * bn * 4 : 0) + 1024;
+}
 
 // Skinny problems (m <= 128: decode batches) are latency- and weight-stream-bound: pick the
 // tile width / K split that gives one wave of up to 296 CTAs (two per SM) with the shortest K
@@ -718,19 +753,20 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         const GemmPlan sk = plan_gemm(GB_M, n, k, true, false);
         if (sk.ks > 1) {
             const uint32_t mt = cdiv(m, GB_M);
-#ifdef AK_MIDM_KSEG2_BN
-            if (mt <= 4 && sk.ks == 2) {   // experiment: two in-CTA K segments instead of a 2-CTA cluster exchange
-                p.kseg = 2; p.ks = 1; p.bn = AK_MIDM_KSEG2_BN;
+            if (mt <= 4 && sk.ks == 2) {
+                // qkv / ffn-up with a prompt or two beside the decode rows: the two K halves as two accumulators
+                // of one CTA (same summation structure as the 2-CTA cluster exchange of the decode plan, without
+                // the exchange); measured 3-6 % off an admission step against the cluster form
+                p.kseg = 2; p.ks = 1; p.bn = 64;
                 uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
                 if (st > G_MAX_STAGES) st = G_MAX_STAGES;
                 p.stages = st < num_kb ? st : num_kb;
                 return p;
             }
-#endif
             if (mt <= 4) {
                 // A prompt or two joining a decode batch: the K chain per CTA, not the flop count, sets the
-                // time (one MMA costs ~150 cycles whatever its width), so keep the cluster split of the
-                // decode plan, with the widest tile that still fits one wave of two CTAs per SM.
+                // time (an MMA of 64 columns or fewer costs the same ~50 cycles), so keep the cluster split of
+                // the decode plan, with the widest tile that still fits one wave of two CTAs per SM.
                 p.ks = sk.ks;
                 p.bn = 16;
                 const uint32_t cands[3] = {64, 32, 16};   // measured: starting from 32 or 16 is slower (1.23 / 1.28 ms against 1.14)
@@ -779,7 +815,9 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         for (int i = 0; i < 3; i++)
             if (cdiv(n, cands[i]) <= slots) { p.bn = cands[i]; break; }
         p.ks = 1;
-        uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
+        const uint32_t ar = a_box_rows(m);
+        uint32_t st = (SMEM_TWO_PER_SM - 1024 - (GB_M - ar) * GB_K * 2) / stage_bytes(p.bn, ar);
+        if (st > G_MAX_STAGES) st = G_MAX_STAGES;
         if (st < 2) st = 2;
         p.stages = st < num_kb ? st : (num_kb ? num_kb : 1);
         return p;
@@ -791,8 +829,10 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
     for (int bi = 0; bi < 3; bi++)
         for (int ki = 0; ki < 4; ki++) {
             const uint32_t bn = bns[bi], ks = kss[ki];
-            // One MMA occupies the tensor core ~150 cycles whatever its N, so a CTA's main loop costs
-            // ~0.3 us per K block; a cluster exchange costs ~1.5 us. Split long K chains (K > 1024), and
+            // One MMA (M = 128 or 64, K = 16) occupies the tensor core 50 cycles for any N <= 64 (64 cycles at
+            // N = 128, 128 at N = 256), and the issuing thread needs ~0.2 us per K block (wait, four MMAs, commit),
+            // so a CTA's main loop costs the same however narrow its tile; a cluster exchange costs ~1.2 us, the
+            // boundary to the next launch ~2 us. Split long K chains (K > 1024), and
             // short ones four ways only when the unsplit grid would cover less than half of the SMs.
             // Other short chains are halved at most (two accumulators still leave 256-column tiles to
             // the large-m plan) and only with tiles of 32 columns or more per exchange.
@@ -803,12 +843,13 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             if (ks > 1 && (ks - 1) * per >= num_kb) continue;  // every CTA of the cluster gets work
             const uint32_t ctas = cdiv(n, bn) * ks;
             if (ctas > slots && !(bi == 2 && ki == 0)) continue;
-            const bool better = per < best_kb || (per == best_kb && ctas > best_ctas);
+            const bool better = per < best_kb || (per == best_kb && ctas > best_ctas);   // more, narrower CTAs measured faster than one wide wave
             if (better) { best_kb = per; best_ctas = ctas; p.bn = bn; p.ks = ks; }
         }
     const uint32_t per = cdiv(num_kb, p.ks);
     const uint32_t red = p.ks > 1 ? GB_M * p.bn * 4 : 0;
-    uint32_t st = (SMEM_TWO_PER_SM - 1024 - red) / stage_bytes(p.bn);
+    const uint32_t ar = a_box_rows(m);
+    uint32_t st = (SMEM_TWO_PER_SM - 1024 - red - (GB_M - ar) * GB_K * 2) / stage_bytes(p.bn, ar);
     if (st > G_MAX_STAGES) st = G_MAX_STAGES;
     if (st < 2) st = 2;
     p.stages = st < per ? st : (per ? per : 1);
@@ -818,8 +859,7 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
 template <int BN, int EPI>
 static int launch_cfg(cudaStream_t st, const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmEpi& ep, uint32_t m, uint32_t n,
                       uint32_t k, const GemmPlan& p) {
-    using C = GemmCfg<BN>;
-    const size_t smem = (size_t)p.stages * C::STAGE_BYTES + (p.ks > 1 ? C::RED_BYTES : 0) + 1024;
+    const size_t smem = gemm_smem_bytes(p.stages, BN, a_box_rows(m), p.ks > 1);
     {
         // per-device "attribute set" flags; the library may be driven from one host thread per GPU
         static size_t attr_set[64] = {};
@@ -989,3 +1029,4 @@ extern "C" int ak_gemm_bf16_ld(void* stream, const void* a, const void* wt, void
     AK_REQUIRE(ldc >= m.n, AK_ERR_INVALID_ARG, "ak_gemm_bf16_ld: ldc (%u) must be at least n (%u)", ldc, m.n);
     return launch_gemm_bf16(as_stream(stream), a, wt, c, m.m, m.n, m.k, epilogue, ldc, false);
 }
+

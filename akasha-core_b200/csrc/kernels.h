@@ -85,9 +85,12 @@ int launch_attn_decode_paged(cudaStream_t st, const void* q, const void* k_pool,
 // (replaces launch_rope_kv_append for rows that hold one decode token each): qkv [rows, 3*heads*head_dim] f32 is the
 // qkv projection's output, position = kv_lens[row] - 1, slot = block_tables[row][pos/16]*16 + pos%16.
 bool attn_decode_fused_supported(uint32_t head_dim);
+// row_order (optional, int32[rows]): a permutation of the rows; CTAs are launched in that order (see attn_decode_row_order).
 int launch_attn_decode_fused(cudaStream_t st, const float* qkv, const float2* rope_table, uint32_t rope_len, void* k_pool, void* v_pool,
-                             const int32_t* block_tables, const int32_t* kv_lens, void* out, void* scratch,
+                             const int32_t* block_tables, const int32_t* kv_lens, const int32_t* row_order, void* out, void* scratch,
                              const ak_attn_decode_params& p, bool counters_are_zero);
+// Host side: the launch order that balances KV bytes over the SMs for these lengths (rows x heads CTAs of one launch).
+void attn_decode_row_order(const int32_t* kv_lens, uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, int32_t* order_out);
 int attn_decode_status(unsigned int* out);  // device status word of the decode kernel
 extern thread_local bool g_attn_early;      // true while the runner launches (cache untouched but for the newest positions)
 

@@ -230,10 +230,14 @@ Runner::~Runner() {
     cudaSetDevice(ctx_->device);
     cudaStreamSynchronize(ctx_->stream);
     if (st2_) cudaStreamSynchronize(st2_);
+    if (st_time_) cudaStreamSynchronize(st_time_);
     for (auto& kv : graphs_) if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
     if (ev_fork_) cudaEventDestroy(ev_fork_);
     if (ev_join_) cudaEventDestroy(ev_join_);
     if (st2_) cudaStreamDestroy(st2_);
+    if (ev_tfork_) cudaEventDestroy(ev_tfork_);
+    if (ev_tjoin_) cudaEventDestroy(ev_tjoin_);
+    if (st_time_) cudaStreamDestroy(st_time_);
     for (Bank& b : banks_) {
         if (b.ev_attn0) cudaEventDestroy(b.ev_attn0);
         if (b.ev_attn1) cudaEventDestroy(b.ev_attn1);
@@ -274,7 +278,8 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
 
     d_.kv_lens = 0;
     d_.out_rows = d_.kv_lens + max_seqs;
-    d_.pf_cu = d_.out_rows + max_seqs;
+    d_.row_order = d_.out_rows + max_seqs;
+    d_.pf_cu = d_.row_order + max_seqs;
     d_.pf_slot = d_.pf_cu + max_seqs + 1;
     d_.pf_pos0 = d_.pf_slot + max_seqs;
     d_.block_tables = d_.pf_pos0 + max_seqs;
@@ -357,6 +362,9 @@ int Runner::init(ak_ctx* ctx, ak_weights* w, uint32_t max_seqs, uint32_t max_seq
     AK_CUDA(cudaStreamCreateWithFlags(&st2_, cudaStreamNonBlocking));
     AK_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
     AK_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
+    AK_CUDA(cudaStreamCreateWithFlags(&st_time_, cudaStreamNonBlocking));
+    AK_CUDA(cudaEventCreateWithFlags(&ev_tfork_, cudaEventDisableTiming));
+    AK_CUDA(cudaEventCreateWithFlags(&ev_tjoin_, cudaEventDisableTiming));
     AK_CUDA(cudaStreamSynchronize(ctx->stream));
     return AK_OK;
 }
@@ -444,24 +452,20 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                     p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
                     p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
                     const bool timed = attn_timing_ && l == 0;
-                    if (timed) {
-                        if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, s, cudaEventRecordExternal));
-                        else AK_CUDA(cudaEventRecord(ev_attn0_, s));
-                    }
+                    if (timed) RC(attn_time_mark(s, ev_attn0_, capturing));
                     // the kernels launched since the descriptor upload wrote nothing of the cache but, at most, each decode
                     // sequence's newest position (unfused) or a prompt's own blocks (the rows of another sequence)
                     g_attn_early = true;
                     if (fuse)
                         rc = launch_attn_decode_fused(s, qkv_, rope_table_, rope_len_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables,
-                                                      d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
+                                                      d_desc_ + d_.kv_lens, d_desc_ + d_.row_order, attn_, attn_scratch_, p, true);
                     else
                         rc = launch_attn_decode_paged(s, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
                     g_attn_early = false;
                     if (rc) return rc;
                     trace_mark("attn_decode");
                     if (timed) {
-                        if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, s, cudaEventRecordExternal));
-                        else AK_CUDA(cudaEventRecord(ev_attn1_, s));
+                        RC(attn_time_mark(s, ev_attn1_, capturing));
                         ev_valid_ = true;
                     }
                 }
@@ -509,17 +513,13 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
                 p.rows = max_seqs_; p.heads = H; p.head_dim = hd; p.block_size = 16; p.max_blocks_per_seq = max_blocks_;
                 p.scale = scale; p.kv_dtype = dt; p.n_splits = n_splits; p.pool_blocks = n_blocks_;
                 const bool timed = attn_timing_ && l == 0;
-                if (timed) {
-                    if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn0_, st, cudaEventRecordExternal));
-                    else AK_CUDA(cudaEventRecord(ev_attn0_, st));
-                }
+                if (timed) RC(attn_time_mark(st, ev_attn0_, capturing));
                 g_attn_early = true;   // the append kernel just before wrote only the newest position of each decode sequence
                 rc = launch_attn_decode_paged(st, qbuf_, k_pool_[l], v_pool_[l], d_desc_ + d_.block_tables, d_desc_ + d_.kv_lens, attn_, attn_scratch_, p, true);
                 g_attn_early = false;
                 if (rc) return rc;
                 if (timed) {
-                    if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev_attn1_, st, cudaEventRecordExternal));
-                    else AK_CUDA(cudaEventRecord(ev_attn1_, st));
+                    RC(attn_time_mark(st, ev_attn1_, capturing));
                     ev_valid_ = true;
                 }
             }
@@ -559,6 +559,24 @@ int Runner::launch_layers(uint32_t T, uint32_t n_pf_rows, uint32_t n_pf_seqs, ui
     }
 #undef RC
     (void)n_pf_rows;
+    if (time_forked_) {  // the timing stream joins the step at its end
+        time_forked_ = false;
+        AK_CUDA(cudaEventRecord(ev_tjoin_, st_time_));
+        AK_CUDA(cudaStreamWaitEvent(st, ev_tjoin_, 0));
+    }
+    return AK_OK;
+}
+
+// A timestamp at "everything launched on `s` so far has completed", taken on a side stream: the kernels on `s`
+// keep their launch-to-launch overlap (an event recorded on `s` itself would sit between two kernels and cut
+// the programmatic edge). Two marks around one launch measure from the completion of its predecessor, the
+// moment its dependency wait returns, to its own completion.
+int Runner::attn_time_mark(cudaStream_t s, cudaEvent_t ev, bool capturing) {
+    AK_CUDA(cudaEventRecord(ev_tfork_, s));
+    AK_CUDA(cudaStreamWaitEvent(st_time_, ev_tfork_, 0));
+    if (capturing) AK_CUDA(cudaEventRecordWithFlags(ev, st_time_, cudaEventRecordExternal));
+    else AK_CUDA(cudaEventRecord(ev, st_time_));
+    time_forked_ = true;
     return AK_OK;
 }
 
@@ -568,6 +586,7 @@ int Runner::run(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_pf_len
     cudaStream_t st = ctx_->stream;
     const uint32_t T = max_seqs_ + n_prefill_rows;
     const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;
+    attn_decode_row_order(h_kv_lens(), max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, h_row_order());
     AK_CUDA(cudaMemcpyAsync(d_desc_, h_desc_, bytes, cudaMemcpyHostToDevice, st));
     // One split count per runner (from the longest sequence it can hold): eager and captured
     // steps then sum in the same order, so a sequence's tokens do not depend on its neighbours.
@@ -613,6 +632,7 @@ int Runner::run_graph(uint32_t n_prefill_rows, uint32_t n_pf_seqs, uint32_t max_
         int32_t* p0 = h_pf_pos0();
         for (uint32_t i = n_pf_seqs; i < seqs_b; i++) { cu[i + 1] = cu[n_pf_seqs]; pfs[i] = 0; p0[i] = 0; }
     }
+    attn_decode_row_order(h_kv_lens(), max_seqs_, heads_l_, w_->cfg.dim / w_->cfg.num_heads, w_->dtype, h_row_order());
     const uint64_t key = ((uint64_t)bank_ << 63) | ((uint64_t)rows_b << 32) | seqs_b;  // a graph bakes its bank's host buffers and events
     const uint32_t T = max_seqs_ + rows_b;
     const size_t bytes = ((size_t)d_.rows + (size_t)T * 4) * 4;

@@ -63,7 +63,7 @@ struct RowInfo {
 };
 
 struct StepDesc {  // offsets (in int32 units) into the descriptor buffer
-    uint32_t kv_lens, out_rows, pf_cu, pf_slot, pf_pos0, block_tables, rows, total;
+    uint32_t kv_lens, out_rows, row_order, pf_cu, pf_slot, pf_pos0, block_tables, rows, total;
 };
 
 class Runner {
@@ -74,6 +74,7 @@ class Runner {
     // Host mirror of the descriptor (pinned). Fill, then run().
     int32_t* h_kv_lens() { return h_desc_ + d_.kv_lens; }
     int32_t* h_out_rows() { return h_desc_ + d_.out_rows; }
+    int32_t* h_row_order() { return h_desc_ + d_.row_order; }   // launch order of the decode attention's rows (filled by run*)
     int32_t* h_pf_cu() { return h_desc_ + d_.pf_cu; }
     int32_t* h_pf_slot() { return h_desc_ + d_.pf_slot; }
     // position of the first prompt row of every prefilled sequence of the step: 0 for a whole prompt, the number of
@@ -184,6 +185,10 @@ class Runner {
     // rows (different sequences: they share nothing until the final norm).
     cudaStream_t st2_ = nullptr;
     cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
+    cudaStream_t st_time_ = nullptr;                       // side stream the attention timestamps are taken on
+    cudaEvent_t ev_tfork_ = nullptr, ev_tjoin_ = nullptr;
+    bool time_forked_ = false;
+    int attn_time_mark(cudaStream_t s, cudaEvent_t ev, bool capturing);
     bool two_streams_ = true;
 };
 

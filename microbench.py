@@ -2,6 +2,7 @@
 
     python microbench.py [attn] [gemm] [norm] [engine] [--iters N] [--small]
                                           [--rows R] [--splits S] [--min-len L] [--max-len L]   (attn only)
+                                          [--n N]                                               (gemm only)
 
   attn : ragged paged decode attention, 1024 sequences, 12 heads x 64, KV lengths U[1,512] (seed 3),
          bf16 K/V ~ N(0,1), block 16.  Reports algorithmic GB/s against the measured HBM peak.
@@ -99,7 +100,8 @@ def bench_gemm(ak, torch, iters, small):
     M, K = (4096 if small else 32768), 768
     _, tf, src = peaks()
     stream = torch.cuda.current_stream().cuda_stream
-    for N in (2304, 3072, 50257):
+    only_n = int(_opt("--n", 0))            # one N only (a profiler capture of the full-size launch)
+    for N in ((only_n,) if only_n else (2304, 3072, 50257)):
         a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
         wt = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
         ldc = (N + 7) // 8 * 8      # a row pitch of whole 16-byte vectors (50257 -> 50264)
