@@ -320,9 +320,15 @@ def main():
                     "h2d_bytes_per_step": (st2["h2d_bytes"] - st["h2d_bytes"]) / args.steps,
                     "d2h_bytes_per_step": (st2["d2h_bytes"] - st["d2h_bytes"]) / args.steps},
             "gpu_launches": int(st["kernel_launches"]),
-            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,4> (layer 0, every decode-only step)",
+            "roofline": {"bound": "hbm", "kernel": "attn_decode_paged_kernel<bf16,64,2> (layer 0, every decode-only step)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind,
+                         # two CUDA events per step, recorded on a side stream of the captured step: "the qkv projection
+                         # before it has completed" and "the attention launch has completed". The kernel keeps its
+                         # launch overlap: its CTAs are resident and have requested their first K/V tiles before the
+                         # first event, so this is the launch's share of the step's critical path, shorter than the
+                         # same launch timed alone (16.1 us, 0.69 of peak: python microbench.py attn --rows 64 --min-len 232)
+                         "timing": "events on a side stream inside the captured step: predecessor complete -> launch complete",
                          # DRAM bytes per launch: 1.059 x the algorithmic bytes, the ratio ncu measured
                          # (dram__bytes_read.sum + dram__bytes_write.sum) on a smaller launch of the same
                          # kernel; traffic grows in proportion to the K/V bytes

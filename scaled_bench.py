@@ -87,7 +87,9 @@ def main():
             "tok/s": thr, "prompt_tokens_rank0": int(sum(len(p) for p in prompts)),
             "rank0": {"steps": st["steps"], "decode_tokens": st["decode_tokens"], "prefill_tokens": st["prefill_tokens"],
                       "attn_GB/s": st["attn_bytes_total"] / max(1e-9, st["attn_ms_total"] * 1e-3) / 1e9,
-                      "attn_us_layer0": 1e3 * st["attn_ms_total"] / max(1, st["attn_launches_timed"])}}))
+                      "attn_us_layer0": 1e3 * st["attn_ms_total"] / max(1, st["attn_launches_timed"]),
+                      # where rank 0's time goes: device time of its steps, host time spent launching them
+                      "gpu_ms_total": st["step_gpu_ms_total"], "launch_host_ms_total": st["launch_host_ms_total"]}}))
     eng.close(); w.close(); ctx.close()
     if world > 1:
         dist.barrier()

@@ -210,6 +210,9 @@ def bf16_round(orc, a):
 
 @pytest.mark.parametrize("m,n,k", [(64, 2304, 768), (1, 768, 768), (64, 768, 3072), (7, 50257, 768), (128, 256, 64), (64, 3072, 768), (64, 8192, 2048), (100, 2048, 8192), (3, 40, 1024),
                                    (300, 520, 200), (1000, 3072, 768), (129, 24, 8), (64, 6144, 2048),
+                                   # activation boxes of 16 / 32 / 64 rows (the ring's activation slots shrink with them), with a K
+                                   # range that fits the ring and one that wraps it
+                                   (16, 3072, 768), (20, 768, 3072), (40, 2304, 768), (20, 512, 8192), (48, 1024, 16384),
                                    # m >= 1024: the CTA-pair (cta_group::2) kernel, incl. ragged last tiles in m, n and k
                                    (1024, 256, 64), (2048, 2304, 768), (1500, 520, 200), (4096, 3072, 768), (1025, 257, 72), (20000, 768, 3072)])
 def test_gemm_bf16_store_f32(ak, orc, torch_cuda, m, n, k):
