@@ -50,6 +50,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ float ex2(float x) {   // 2^x, hardware approximation (2 ulp), ex2(-inf) = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -171,7 +176,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     float o[HD];
 #pragma unroll
     for (int d = 0; d < HD; d++) o[d] = 0.0f;
-    float m_run = -INFINITY, l_run = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f;   // m_run in the base-2 domain (score * scale * log2 e)
+    const float sl2 = scale * 1.4426950408889634f;
     const uint32_t qi = pos0 + q0 + tid;  // this thread's query position
     bool ok = true;
 
@@ -209,37 +215,48 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 for (uint32_t i = tid; i < chunks; i += THREADS)
                     *reinterpret_cast<uint4*>(v_sm + hf * (BKV * 128) + (first + i / 8) * 128 + (i % 8) * 16) = make_uint4(0, 0, 0, 0);
         }
-        // ---- pass 1: row maximum of the masked, scaled scores
+        // A tile needs the per-element mask only if it reaches past the sequence end or past the first query of this
+        // CTA's tile (the diagonal); every other tile is fully visible to every row. CTA-uniform.
+        const bool need_mask = (k0 + BKV > kv_len) || (k0 + BKV - 1 > pos0 + q0);
+        // ---- pass 1: row maximum of the raw scores (scale > 0: scaling commutes with the maximum)
         float mx = -INFINITY;
 #pragma unroll 1
-        for (uint32_t c0 = 0; c0 < BKV; c0 += 16) {
-            uint32_t r[16];
+        for (uint32_t c0 = 0; c0 < BKV; c0 += 32) {
+            uint32_t r[32];
             tmem_ld16(tmem_s + lane_addr + c0, r);
+            tmem_ld16(tmem_s + lane_addr + c0 + 16, r + 16);
             tmem_ld_wait();
+            if (need_mask) {
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const uint32_t kj = k0 + c0 + j;
-                if (kj <= qi && kj < kv_len) mx = fmaxf(mx, __uint_as_float(r[j]) * scale);
+                for (int j = 0; j < 32; j++) {
+                    const uint32_t kj = k0 + c0 + j;
+                    if (kj <= qi && kj < kv_len) mx = fmaxf(mx, __uint_as_float(r[j]));
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; j++) mx = fmaxf(mx, __uint_as_float(r[j]));
             }
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float corr = (m_new == -INFINITY) ? 1.0f : __expf(m_run - m_new);
-        // ---- pass 2: P = exp(s - m_new) -> bf16 -> shared (swizzled K-major rows of 128 bytes)
+        // running maximum and exponentials in base 2: p = 2^(s * scale * log2(e) - m), one FMA and one ex2 per score
+        const float m_new = fmaxf(m_run, mx * sl2);
+        const float corr = (m_new == -INFINITY) ? 1.0f : ex2(m_run - m_new);
+        // ---- pass 2: P = 2^(s * sl2 - m_new) -> bf16 -> shared (swizzled K-major rows of 128 bytes)
         float rs = 0.0f;
 #pragma unroll 1
-        for (uint32_t c0 = 0; c0 < BKV; c0 += 16) {
-            uint32_t r[16];
+        for (uint32_t c0 = 0; c0 < BKV; c0 += 32) {
+            uint32_t r[32];
             tmem_ld16(tmem_s + lane_addr + c0, r);
+            tmem_ld16(tmem_s + lane_addr + c0 + 16, r + 16);
             tmem_ld_wait();
-            uint32_t pk[8];
+            uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 16; j += 2) {
+            for (int j = 0; j < 32; j += 2) {
                 float p2[2];
 #pragma unroll
                 for (int e = 0; e < 2; e++) {
+                    const float pe = ex2(fmaf(__uint_as_float(r[j + e]), sl2, -m_new));
                     const uint32_t kj = k0 + c0 + j + e;
-                    const bool valid = kj <= qi && kj < kv_len;
-                    p2[e] = valid ? __expf(__uint_as_float(r[j + e]) * scale - m_new) : 0.0f;
+                    p2[e] = (!need_mask || (kj <= qi && kj < kv_len)) ? pe : 0.0f;
                 }
                 bf162 v2 = __floats2bfloat162_rn(p2[0], p2[1]);
                 // the running sum uses the ROUNDED probabilities, the ones the tensor core multiplies
@@ -247,9 +264,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                 pk[j / 2] = *reinterpret_cast<uint32_t*>(&v2);
             }
             uint8_t* p_row = p_sm + (c0 / 64) * (BQ * 128) + tid * 128;  // slab of 64 keys, this thread's row
-            const uint32_t ch = (c0 % 64) / 8;                           // two 16-byte chunks per 16 columns
-            *reinterpret_cast<uint4*>(p_row + (((ch) ^ (tid & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(p_row + (((ch + 1) ^ (tid & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            const uint32_t ch = (c0 % 64) / 8;                           // four 16-byte chunks per 32 columns
+#pragma unroll
+            for (uint32_t q4 = 0; q4 < 4; q4++)
+                *reinterpret_cast<uint4*>(p_row + (((ch + q4) ^ (tid & 7)) << 4)) = make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
         }
         l_run = l_run * corr + rs;
         m_run = m_new;

@@ -179,6 +179,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-config1", action="store_true", help="print the reference CPU configuration's numbers and exit")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pin", action="store_true", help="multi-rank runs: do not pin each rank to its own host cores")
     ap.add_argument("--sync-steps", action="store_true", help="read every step's tokens before launching the next one")
     ap.add_argument("--chunked-prefill", action="store_true",
                     help="prefill a prompt admitted while others decode in 64-row chunks that ride in the decode launches")
@@ -187,6 +188,15 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    # Several ranks on one host: give each its own share of the host cores before any thread is created, so that one
+    # rank's launch thread is never descheduled for another's (a host-side setting of this process, not of a GPU).
+    cores_per_rank = None
+    if world > 1 and not args.no_pin and args.impl != "reference" and hasattr(os, "sched_setaffinity"):
+        cpus = sorted(os.sched_getaffinity(0))
+        per = len(cpus) // world
+        if per >= 1:
+            os.sched_setaffinity(0, set(cpus[local_rank * per:(local_rank + 1) * per]))
+            cores_per_rank = per
     ak = entry.load_package()
 
     if args.cpu_config1:
@@ -342,7 +352,7 @@ def main():
                        "graph_launches": st["graph_launches"], "eager_steps": st["eager_steps"],
                        "host_counted_launches": int(eager_launches), "engine_steps_per_job": steps_per_job,
                        "cuda_graph": not args.no_graph, "async_steps": not args.sync_steps,
-                       "chunked_prefill": args.chunked_prefill,
+                       "chunked_prefill": args.chunked_prefill, "host_cores_per_rank": cores_per_rank,
                        # rank 0, per job (one pass over the 256 sequences): where the time goes
                        "gpu_ms_per_job": st["step_gpu_ms_total"] / args.steps,
                        "launch_host_ms_per_job": st["launch_host_ms_total"] / args.steps,

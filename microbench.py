@@ -11,6 +11,7 @@
   engine : steady-state decode steps of the 162M engine with 64 ragged sequences in flight
          (not in the default set; the launch sequence to hand to a profiler).
   session : batch-1 prefill + greedy decode through the session API, fp32 and bf16 (not in the default set).
+  prefill : causal prefill attention over the paged pools, both model shapes (not in the default set). Reports TFLOP/s.
 
 `--small` shrinks every case (for a profiler capture: inputs stay above the 126 MB L2 where it
 matters, a few launches, well under a GB on the device).
@@ -146,6 +147,43 @@ def bench_skinny(ak, torch, iters, small):
     return res
 
 
+def bench_prefill(ak, torch, iters, small):
+    """Causal prefill attention over the paged pools (tcgen05 kernel), the two model shapes: tensor-core flops
+    4 * H * hd * sum(P^2 / 2) per launch against the measured bf16 peak."""
+    res = []
+    _, tf, src = peaks()
+    stream = torch.cuda.current_stream().cuda_stream
+    g = torch.Generator(device="cuda").manual_seed(7)
+    cases = [("162M: 12 heads x 64, 32 prompts of 448", 12, 64, [448] * 32),
+             ("162M: 12 heads x 64, 8 prompts of 2048", 12, 64, [2048] * (2 if small else 8)),
+             ("1.4B: 16 heads x 128, 8 prompts of 2048", 16, 128, [2048] * (2 if small else 8)),
+             ("1.4B: 16 heads x 128, ragged U[128,3072] x 16", 16, 128, [int(v) for v in ak.uniform_ints(4 if small else 16, 128, 3072, seed=5)])]
+    for name, H, hd, lens in cases:
+        dim, n = H * hd, len(lens)
+        max_blocks = (max(lens) + 15) // 16
+        n_blocks = n * max_blocks
+        kp = torch.randn(n_blocks, H, 16, hd, device="cuda", generator=g).bfloat16()
+        vp = torch.randn(n_blocks, H, 16, hd, device="cuda", generator=g).bfloat16()
+        tables = torch.randperm(n_blocks, device="cuda", generator=g).to(torch.int32).reshape(n, max_blocks)
+        cu = np.zeros(n + 1, np.int32)
+        cu[1:] = np.cumsum(lens)
+        total = int(cu[-1])
+        q = torch.randn(total, dim, device="cuda", generator=g).bfloat16()
+        out = torch.empty_like(q)
+        dcu = torch.from_numpy(cu).cuda()
+        slot = torch.arange(n, dtype=torch.int32, device="cuda")
+        scale = 1.0 / float(np.sqrt(hd))
+        fn = lambda: ak.ops.attn_prefill_paged(q, kp, vp, tables, max_blocks, dcu, slot, out, n, max(lens), total, H, hd, scale,
+                                               ak.AK_BF16, n_blocks, stream)
+        ms = timed(torch, fn, max(3, iters // 4))
+        fl = 4.0 * H * hd * sum(L * (L + 1) / 2 for L in lens)      # QK^T and PV over the causal half
+        t = fl / (ms * 1e-3) / 1e12
+        res.append({"kernel": "prefill_tc_kernel (tcgen05 causal attention)", "case": name, "prompt_tokens": total, "ms": ms,
+                    "TFLOP/s": t, "peak_TFLOP/s": tf, "frac": t / tf, "peak_source": src})
+        del kp, vp, q, out
+    return res
+
+
 def bench_norm(ak, torch, iters, small):
     rows, size, hd = (8192 if small else 32768), 768, 64
     nbuf = 4  # rotate buffers: 4 x (100 MB in + 50 MB out) > L2
@@ -263,13 +301,13 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a CUDA device")
     ak = entry.load_package()
-    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine", "skinny", "session")]
+    args = [a for a in sys.argv[1:] if a in ("attn", "gemm", "norm", "engine", "skinny", "session", "prefill")]
     iters = int(_opt("--iters", 20))
     small = "--small" in sys.argv
     which = args or ["attn", "gemm", "norm"]
     torch.cuda.set_device(0)
     for w in which:
-        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine, "skinny": bench_skinny, "session": bench_session}[w](ak, torch, iters, small)
+        r = {"attn": bench_attn, "gemm": bench_gemm, "norm": bench_norm, "engine": bench_engine, "skinny": bench_skinny, "session": bench_session, "prefill": bench_prefill}[w](ak, torch, iters, small)
         for line in (r if isinstance(r, list) else [r]):
             print(json.dumps(line))
     torch.cuda.synchronize()
