@@ -106,8 +106,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     using C = Cfg<HD, BKV>;
     pdl_wait();
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_bar, kv_bar[2], s_bar, pv_bar;
-    __shared__ uint32_t tmem_base_sm, fail_flag;
 
     const uint32_t seq = blockIdx.z, h = blockIdx.y, q0 = blockIdx.x * BQ;
     // len query rows at positions pos0 .. pos0 + len - 1 (pos0 > 0: a later chunk of a prompt whose first pos0
@@ -125,6 +123,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     uint8_t* q_sm = smem;
     uint8_t* kv_sm = q_sm + C::Q_BYTES;            // [buf][K | V] each KV_BYTES
     uint8_t* p_sm = kv_sm + 4 * C::KV_BYTES;
+    // The barriers live in the dynamic allocation too, behind the tiles: with no static shared memory at all the
+    // 112 KB of tiles + 1 KB of alignment room are exactly what lets TWO CTAs share an SM (228 KB, 1 KB reserved per
+    // CTA); 48 bytes of static variables made it one. The room left for alignment is 1024 - 64 bytes, enough for any
+    // base that is 64-byte aligned (with nothing static in front of it the base is the start of the CTA's window).
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_sm + C::P_BYTES);
+    uint64_t& q_bar = bars[0];
+    uint64_t* kv_bar = bars + 1;   // [2]
+    uint64_t& s_bar = bars[3];
+    uint64_t& pv_bar = bars[4];
+    uint32_t& tmem_base_sm = *reinterpret_cast<uint32_t*>(bars + 5);
+    uint32_t& fail_flag = *(reinterpret_cast<uint32_t*>(bars + 5) + 1);
+    if ((uintptr_t)(smem - smem_raw) > 1024 - 64) {   // cannot happen with the alignment above; never run past the allocation
+        if (tid == 0) atomicExch(&g_prefill_tc_status, 9u);
+        pdl_trigger();
+        return;
+    }
 
     if (tid == 0) {
         mbar_init(&q_bar, 1); mbar_init(&kv_bar[0], 1); mbar_init(&kv_bar[1], 1); mbar_init(&s_bar, 1); mbar_init(&pv_bar, 1);
@@ -145,14 +159,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const uint32_t q_hi = pos0 + ((q0 + BQ - 1 < len - 1) ? q0 + BQ - 1 : len - 1);   // position of the tile's last query
     const uint32_t n_tiles = q_hi / BKV + 1;
 
-    uint32_t loaded = 0, consumed = 0;  // thread 0: K/V tiles requested / waited for
-    auto load_kv = [&](uint32_t t) {  // thread 0
+    uint32_t loaded = 0, consumed = 0;  // warp 0: K/V tiles requested / waited for
+    // Called by the whole of warp 0: lane 0 arms the barrier, then one lane per 16-position block looks up its block
+    // and requests its K and V rows (a single thread issuing all 16 loads of a tile one after the other spent
+    // ~1200 cycles on it, on the path of every tile).
+    auto load_kv = [&](uint32_t t) {
         loaded = t + 1;
-        const uint32_t b = t & 1;
+        const uint32_t b = t & 1, lane = tid & 31;
         uint8_t* k_dst = kv_sm + (size_t)b * 2 * C::KV_BYTES;
         uint8_t* v_dst = k_dst + C::KV_BYTES;
-        mbar_expect_tx(&kv_bar[b], 2 * C::KV_BYTES);
-        for (uint32_t blk = 0; blk < BKV / BS; blk++) {
+        if (lane == 0) mbar_expect_tx(&kv_bar[b], 2 * C::KV_BYTES);
+        __syncwarp();
+        if (lane < BKV / BS) {
+            const uint32_t blk = lane;
             const uint32_t pos = t * BKV + blk * BS;
             // blocks past the sequence end are fetched from its first block: finite data, masked out below
             const uint32_t bidx = pos < kv_len ? pos / BS : 0;
@@ -165,11 +184,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
     };
 
-    if (tid == 0) {
-        mbar_expect_tx(&q_bar, C::Q_BYTES);
+    if (warp == 0) {
+        if (tid == 0) {
+            mbar_expect_tx(&q_bar, C::Q_BYTES);
 #pragma unroll
-        for (int hf = 0; hf < C::HALVES; hf++)
-            tma_load_2d(q_sm + hf * (BQ * 128), &tmQ, (int32_t)(h * HD + hf * 64), (int32_t)(row0 + q0), &q_bar);
+            for (int hf = 0; hf < C::HALVES; hf++)
+                tma_load_2d(q_sm + hf * (BQ * 128), &tmQ, (int32_t)(h * HD + hf * 64), (int32_t)(row0 + q0), &q_bar);
+        }
         load_kv(0);
     }
 
@@ -185,11 +206,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const uint32_t b = t & 1, ph = t & 1;
         uint8_t* k_sm = kv_sm + (size_t)b * 2 * C::KV_BYTES;
         uint8_t* v_sm = k_sm + C::KV_BYTES;
-        if (tid == 0) {
-            if (t + 1 < n_tiles) load_kv(t + 1);  // the other buffer was released by pv_bar of tile t-1
+        if (warp == 0) {
+          if (tid == 0) {
             bool w = (t > 0) || mbar_wait(&q_bar, 0);
             w = w && mbar_wait(&kv_bar[b], (t >> 1) & 1u);
-            consumed = t + 1;
             if (!w) atomicExch(&fail_flag, 1u);
             tc_fence_after();
             // S[128 x 64] = Q[128 x HD] . K[64 x HD]^T
@@ -200,6 +220,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
                        idesc(BQ, BKV, 0), kk != 0);
             }
             tc_commit(&s_bar);
+          }
+          // the next tile's K/V, requested while the tensor core works on S (the other buffer was released by pv_bar of
+          // tile t-1, which every thread has waited for)
+          __syncwarp();
+          consumed = t + 1;
+          if (t + 1 < n_tiles) load_kv(t + 1);
         }
         bool good = mbar_wait(&s_bar, ph);
         if (!good) atomicExch(&fail_flag, 2u);
