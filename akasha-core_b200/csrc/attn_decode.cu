@@ -641,7 +641,7 @@ static uint32_t wave_slots(uint32_t head_dim, uint32_t kv_dtype, uint32_t stages
     uint32_t per_sm = (227 * 1024) / smem;
     if (per_sm > 6) per_sm = 6;
     if (per_sm < 1) per_sm = 1;
-    return 148 * per_sm;
+    return B200_SMS * per_sm;
 }
 uint32_t attn_decode_pick_splits(uint32_t rows, uint32_t heads, uint32_t head_dim, uint32_t kv_dtype, uint32_t max_kv_len) {
     const uint64_t items = (uint64_t)rows * heads;
@@ -718,7 +718,7 @@ void attn_decode_row_order(const int32_t* kv_lens, uint32_t rows, uint32_t heads
     // positions y in the order in which the sorted rows are dealt: by level, alternating direction
     std::vector<uint32_t> pos(rows);
     for (uint32_t y = 0; y < rows; y++) pos[y] = y;
-    auto level = [&](uint32_t y) { return (uint32_t)(((uint64_t)y * heads) / 148); };
+    auto level = [&](uint32_t y) { return (uint32_t)(((uint64_t)y * heads) / B200_SMS); };
     std::stable_sort(pos.begin(), pos.end(), [&](uint32_t a, uint32_t b) {
         const uint32_t la = level(a), lb = level(b);
         if (la != lb) return la < lb;

@@ -12,6 +12,9 @@
 
 namespace ak {
 
+// This library is written for one part: B200, 148 SMs (two dies of 74). Grid sizing and launch plans use the figure.
+constexpr uint32_t B200_SMS = 148;
+
 // ---- host-side error plumbing -------------------------------------------------------------
 void set_error(const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what, const char* file, int line);

@@ -333,7 +333,7 @@ __global__ void silu_kernel(float* __restrict__ x, size_t n) {
 }
 int launch_silu(cudaStream_t st, float* x, uint64_t n) {
     if (n == 0) return AK_OK;
-    unsigned blocks = (unsigned)(cdiv64(n, 256) < 148u * 16 ? cdiv64(n, 256) : 148u * 16);
+    unsigned blocks = (unsigned)(cdiv64(n, 256) < B200_SMS * 16 ? cdiv64(n, 256) : B200_SMS * 16);
     silu_kernel<<<blocks, 256, 0, st>>>(x, n);
     AK_COUNT_LAUNCH();
     AK_CHECK_LAUNCH();
@@ -520,7 +520,7 @@ __global__ void bf16_to_f32_kernel(const bf16* __restrict__ s, float* __restrict
 }
 static unsigned stride_blocks(size_t n) {
     size_t b = cdiv64(n, 256);
-    return (unsigned)(b < 148u * 32 ? b : 148u * 32);
+    return (unsigned)(b < B200_SMS * 32 ? b : B200_SMS * 32);
 }
 int launch_f32_to_bf16(cudaStream_t st, const float* src, void* dst, uint64_t n) {
     if (!n) return AK_OK;

@@ -785,7 +785,7 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             // widest tile whose accumulators fit TMEM (kseg * bn <= 512 columns); narrower while
             // the grid would leave most SMs idle
             p.bn = 512 / sk.ks > 256 ? 256 : 512 / sk.ks;
-            while (p.bn > 32 && (uint64_t)mt * cdiv(n, p.bn) < 148) p.bn /= 2;
+            while (p.bn > 32 && (uint64_t)mt * cdiv(n, p.bn) < B200_SMS) p.bn /= 2;
             uint32_t st = (SMEM_ONE_PER_SM - 1024) / stage_bytes(p.bn);
             if (st > G_MAX_STAGES) st = G_MAX_STAGES;
             if (p.bn <= 64 && st > 6) st = 6;
@@ -798,7 +798,7 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
         const uint32_t cands[5] = {256, 128, 64, 32, 16};
         p.bn = 16;
         for (int i = 0; i < 5; i++)
-            if ((uint64_t)mt * cdiv(n, cands[i]) >= 148) { p.bn = cands[i]; break; }
+            if ((uint64_t)mt * cdiv(n, cands[i]) >= B200_SMS) { p.bn = cands[i]; break; }
         p.ks = 1;
         // Two CTAs per SM (one's epilogue under the other's main loop) beat one CTA with a deeper ring.
         uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
@@ -836,7 +836,7 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
             // short ones four ways only when the unsplit grid would cover less than half of the SMs.
             // Other short chains are halved at most (two accumulators still leave 256-column tiles to
             // the large-m plan) and only with tiles of 32 columns or more per exchange.
-            const bool short_k_ok = cdiv(n, 16) * 2 <= 148;
+            const bool short_k_ok = cdiv(n, 16) * 2 <= B200_SMS;
             if (ks > 1 && num_kb <= 16 && !short_k_ok && (ks > 2 || bn < 32)) continue;
             if (ks > 1 && (!allow_split || ks * 2 > num_kb || (bn / ks) % 4 != 0)) continue;
             const uint32_t per = cdiv(num_kb, ks);
