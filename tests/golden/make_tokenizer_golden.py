@@ -5,8 +5,8 @@ sample strings written for this test, and the text it decodes them back to.
 
     python tests/golden/make_tokenizer_golden.py [path/to/tokenizer.json]
 
-Needs the `tokenizers` package and the reference's tokenizer.json (default $AKASHA_TOKENIZER or
-/root/reference/tokenizer.json); only ids and strings are stored, not the vocabulary.
+Needs the `tokenizers` package and the reference's tokenizer.json (the argument, else the AKASHA_TOKENIZER
+environment variable, else the reference checkout's copy); only ids and strings are stored, not the vocabulary.
 """
 import json
 import os

@@ -3,7 +3,7 @@ of the reference's `--chat` (src/tokenizer.rs:4-49).
 
 Two layers. (1) A tiny tokenizer.json written here exercises every step of the algorithm with answers
 that can be worked out by hand. (2) Where the reference's tokenizer.json is available
-($AKASHA_TOKENIZER, or /root/reference/tokenizer.json), the implementation is held to
+(the AKASHA_TOKENIZER environment variable, else the reference checkout's copy), the implementation is held to
 tests/golden/tokenizer_golden.json: ids and round-trip text that the Hugging Face `tokenizers` library
 (the crate the reference wraps) produced from that file for the sample strings of
 tests/golden/make_tokenizer_golden.py.
