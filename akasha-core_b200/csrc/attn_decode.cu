@@ -218,10 +218,12 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     const uint32_t row = fz.row_order ? (uint32_t)fz.row_order[blockIdx.y] : blockIdx.y;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t* table = block_tables + (size_t)row * max_blocks;
-    // Unsplit launches know their blocks' table entries without the length: fetch both at once (one memory
-    // latency instead of two before the first tile can be requested). Entries past the sequence's end are never used.
+    // Lane j holds the block-table entry of this warp's j-th tile (the first 32 tiles of a warp: 2048 positions), so
+    // no table read sits between the end of one tile and the request for the next. Unsplit launches know which
+    // entries those are without the length: they are fetched together with it (one memory latency instead of two
+    // before the first tile can be requested). Entries past the sequence's end are never used.
     uint32_t my_blk = 0;
-    if (n_splits == 1 && lane < (uint32_t)C::STAGES && warp + lane * DEC_WARPS < max_blocks) my_blk = (uint32_t)table[warp + lane * DEC_WARPS];
+    if (n_splits == 1 && warp + lane * DEC_WARPS < max_blocks) my_blk = (uint32_t)table[warp + lane * DEC_WARPS];
     const int32_t kv_len = kv_lens[row];
 
     // block range of this split
@@ -264,8 +266,10 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
     // known to be complete
     const uint32_t pre = nmine < (uint32_t)C::STAGES ? nmine : (uint32_t)C::STAGES;
     bool deferred = false;
+    if (n_splits != 1 && lane < nmine) my_blk = (uint32_t)table[first + lane * DEC_WARPS];
+    // physical block of this warp's j-th tile (j warp-uniform)
+    auto blk_of = [&](uint32_t j) { return j < 32 ? __shfl_sync(0xffffffffu, my_blk, j) : (uint32_t)table[first + j * DEC_WARPS]; };
     if (lane < pre) {
-        if (n_splits != 1) my_blk = (uint32_t)table[first + lane * DEC_WARPS];
         deferred = early && !fused && (first + lane * DEC_WARPS + 1 == nblk);
         if (!deferred) issue(lane, my_blk);
     }
@@ -366,7 +370,7 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
             const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
             if (fused && blk_idx + 1 == nblk)
-                append_new((uint32_t)table[blk_idx], my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
+                append_new(blk_of(i), my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
             if (n_valid < DEC_BS) {
                 // rows past the end of the sequence may hold anything (their probability is 0, but
                 // 0 * NaN would poison the tensor-core sum): clear them in the V tile
@@ -425,7 +429,10 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 mma_bf16_16816(acc[2 * jj + 1], p01, p01, p23, p23, vb[2], vb[3]);
             }
             __syncwarp();
-            if (i + C::STAGES < nmine && lane == 0) issue(i + C::STAGES, (uint32_t)table[first + (i + C::STAGES) * DEC_WARPS]);
+            if (i + C::STAGES < nmine) {   // warp-uniform
+                const uint32_t nb = blk_of(i + C::STAGES);
+                if (lane == 0) issue(i + C::STAGES, nb);
+            }
         }
         // rows of the accumulator are replicas: quad 0 (lanes 0-3) publishes the warp's output
         if (lane < 4) {
@@ -471,7 +478,7 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
             const int32_t n_valid_raw = kv_len - (int32_t)(blk_idx * DEC_BS);
             const uint32_t n_valid = n_valid_raw >= DEC_BS ? DEC_BS : (uint32_t)n_valid_raw;
             if (fused && blk_idx + 1 == nblk)
-                append_new((uint32_t)table[blk_idx], my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
+                append_new(blk_of(i), my_smem + (size_t)s * C::STAGE_BYTES, my_smem + (size_t)s * C::STAGE_BYTES + C::TILE_BYTES);
 
             // ---- scores: position p, this lane's half of every 128-byte group
             float sc = 0.0f;
@@ -530,7 +537,10 @@ attn_decode_paged_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_c
                 }
             }
             __syncwarp();
-            if (i + C::STAGES < nmine && lane == 0) issue(i + C::STAGES, (uint32_t)table[first + (i + C::STAGES) * DEC_WARPS]);
+            if (i + C::STAGES < nmine) {   // warp-uniform
+                const uint32_t nb = blk_of(i + C::STAGES);
+                if (lane == 0) issue(i + C::STAGES, nb);
+            }
         }
 #pragma unroll
         for (int e = 0; e < C::EPL; e++) sm_acc[warp][lane * C::EPL + e] = acc[e];
