@@ -769,7 +769,7 @@ static GemmPlan plan_gemm(uint32_t m, uint32_t n, uint32_t k, bool allow_split, 
                 // of one CTA (same summation structure as the 2-CTA cluster exchange of the decode plan, without
                 // the exchange); measured 3-6 % off an admission step against the cluster form
                 p.kseg = 2; p.ks = 1; p.bn = 64;
-                uint32_t st = (SMEM_TWO_PER_SM - 1024) / stage_bytes(p.bn);
+                uint32_t st = (SMEM_THREE_PER_SM - 1024) / stage_bytes(p.bn);   // three per SM: these run beside the decode rows' chain
                 if (st > G_MAX_STAGES) st = G_MAX_STAGES;
                 p.stages = st < num_kb ? st : num_kb;
                 return p;
