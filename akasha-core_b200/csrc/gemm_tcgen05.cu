@@ -97,6 +97,18 @@ __device__ __forceinline__ void cluster_sync_all() {
     cluster_arrive_all();
     cluster_wait_all();
 }
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+// 16 bytes into a peer CTA's shared memory; on arrival they are counted (complete_tx) on a barrier of that CTA
+__device__ __forceinline__ void st_async_v4(uint32_t dst_cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t bar_cluster_addr) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(dst_cluster_addr),
+                 "r"(a), "r"(b), "r"(c), "r"(d), "r"(bar_cluster_addr)
+                 : "memory");
+}
 
 template <int BN> struct GemmCfg {
     static constexpr int B_BYTES = BN * GB_K * 2;   // weight tile of a stage; a multiple of 1024 for every BN % 8 == 0
@@ -257,7 +269,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // share the launch.
     using C = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t full_bar[G_MAX_STAGES], empty_bar[G_MAX_STAGES], acc_bar;
+    __shared__ uint64_t full_bar[G_MAX_STAGES], empty_bar[G_MAX_STAGES], acc_bar, xch_bar;
     __shared__ uint32_t tmem_base_sm;
     __shared__ uint32_t fail_flag;
 
@@ -285,8 +297,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < stages; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(&acc_bar, 1);
+        mbar_init(&xch_bar, 1);
         fail_flag = 0;
         mbar_fence_init();
+        if (SPLIT) {
+            // the partial slices the peers will push into this CTA's exchange buffer: SL columns of every valid row
+            // from each of the other ks - 1 CTAs (armed before the start barrier below, which the peers pass first)
+            const uint32_t rows_here = (m - m0 < (uint32_t)GB_M) ? m - m0 : (uint32_t)GB_M;
+            mbar_expect_tx(&xch_bar, (ks - 1) * rows_here * ((uint32_t)BN / ks) * 4u);
+        }
         tma_prefetch_desc(&tmA);
         tma_prefetch_desc(&tmB);
     }
@@ -443,14 +462,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll
                     for (uint32_t j = 0; j < 16; j += 4) {
                         const uint32_t col = c0 + j, dest = col / SL, off = col - dest * SL;
-                        float* peer = cluster.map_shared_rank(red, dest);
-                        *reinterpret_cast<uint4*>(peer + ((size_t)rank * a_rows + trow) * SL + off) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        float* slot = red + ((size_t)rank * a_rows + trow) * SL + off;
+                        if (dest == rank) {   // my own slice: read back by this same thread
+                            *reinterpret_cast<uint4*>(slot) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        } else {              // a peer's: an asynchronous store that is counted on the peer's exchange barrier
+                            st_async_v4(map_to_cta(smem_u32(slot), dest), r[j], r[j + 1], r[j + 2], r[j + 3], map_to_cta(smem_u32(&xch_bar), dest));
+                        }
                     }
                 }
             }
         }
-        tc_fence_before();
-        cluster_sync_all();  // every partial slice has landed in its owner's shared memory
+        // Every peer's slices for this CTA have landed when the exchange barrier's byte count is met: no cluster-wide
+        // barrier (0.75 us). A CTA leaves only after it has received everything addressed to it, so nobody writes
+        // into a CTA that is gone.
+        if (warp >= 2 && got) {
+            bool landed = mbar_wait(&xch_bar, 0);
+            if (!landed && lane == 0) atomicExch(&fail_flag, 6u);
+            got = __all_sync(0xffffffffu, landed);
+        }
         if (warp >= 2 && got && row < m) {
 #pragma unroll 1
             for (uint32_t j = 0; j < SL; j += 4) {
@@ -502,12 +531,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// shared::cluster address of the same shared-memory variable in CTA `rank` of the cluster
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
