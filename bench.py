@@ -306,6 +306,14 @@ def main():
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms_max, e2e_ms_max = times.tolist()
+    # per rank, so that a scaling loss can be attributed: the device-timed leg (ms per job), the GPU time of the
+    # rank's own steps and the host time it spent launching them
+    mine = torch.tensor([dev_ms / args.steps, st["step_gpu_ms_total"] / args.steps, st["launch_host_ms_total"] / args.steps],
+                        dtype=torch.float64, device="cuda")
+    per_rank = [mine.clone() for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per_rank, mine)
+    per_rank = [[round(v, 2) for v in t.tolist()] for t in per_rank]
     total_gen = gen_per_job * args.steps * world
     value = total_gen / (dev_ms_max / 1e3)
     e2e_value = total_gen / (e2e_ms_max / 1e3)
@@ -356,6 +364,7 @@ def main():
                        # rank 0, per job (one pass over the 256 sequences): where the time goes
                        "gpu_ms_per_job": st["step_gpu_ms_total"] / args.steps,
                        "launch_host_ms_per_job": st["launch_host_ms_total"] / args.steps,
+                       "per_rank_ms_per_job": {"columns": ["device_timed_leg", "gpu_steps", "launch_host"], "ranks": per_rank},
                        "ids_checked_between_legs": list(CHECK)},
         }
         if world == 1 and not args.no_cpu_baseline:
